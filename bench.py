@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only NAME]
+
+Prints ONE JSON line. A "step" is one pass of the primary workload (BASELINE.json configs[1]:
+causal bf16 prefill B=4, Hq=Hkv=32, S=2048, d=128 with fp32 LSE). With N > 1 (torchrun, one rank
+per GPU) every rank owns 32 query/KV heads of a 32*N-head layer (weak scaling), runs the same
+kernel on its shard and the outputs are joined by one all-gather along the head axis, inside the
+timed region. The other BASELINE.json configs are measured as well and reported under
+"workloads" (each with its own roofline object); "--only NAME" restricts the run to one of them.
+
+`--impl reference` times the CPU restatement of luma-cpu's math-path attention (oracle/) on the
+host cores: the reference's own implementation of this path is Rust and cannot be built with
+this image's toolchains.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NOMINAL_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {**FALLBACK_PEAKS, "source": "fallback"}
+
+
+def causal_flops(b, hq, sq, skv, d, start_pos=0):
+    """4*d FLOPs per visible (query, key) pair; row i sees min(skv, start_pos + i + 1) keys."""
+    i = np.arange(sq, dtype=np.int64)
+    vis = np.minimum(skv, start_pos + i + 1).sum()
+    return int(4 * d * b * hq * int(vis))
+
+
+# ------------------------------------------------------------------------------------------
+# clocks sampling
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+# ------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------
+def make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in=1.0):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    q = (torch.randn(b, s, hq, d, generator=g, device=dev, dtype=torch.float32) * scale_in).to(torch.bfloat16)
+    k = (torch.randn(b, s, hkv, d, generator=g, device=dev, dtype=torch.float32) * scale_in).to(torch.bfloat16)
+    v = (torch.randn(b, s, hkv, d, generator=g, device=dev, dtype=torch.float32) * scale_in).to(torch.bfloat16)
+    return q, k, v
+
+
+def make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool_pages, seed):
+    rng = np.random.Generator(np.random.Philox(seed))
+    lens = rng.integers(lo, hi + 1, size=batch).astype(np.int32)
+    need = (lens.astype(np.int64) + page - 1) // page
+    if pool_pages is None:
+        pool_pages = int(need.sum() * 1.15) + 1
+    assert need.sum() <= pool_pages
+    perm = rng.permutation(pool_pages).astype(np.int32)
+    max_blocks = int(math.ceil(hi / page))
+    table = np.full((batch, max_blocks), -1, dtype=np.int32)
+    pos = 0
+    for s_, n in enumerate(need):
+        table[s_, :n] = perm[pos:pos + n]
+        pos += int(n)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    kc = torch.empty(pool_pages, page, hkv, d, device=dev, dtype=torch.bfloat16)
+    vc = torch.empty_like(kc)
+    step = 4096
+    for i in range(0, pool_pages, step):
+        n = min(step, pool_pages - i)
+        kc[i:i + n] = torch.randn(n, page, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        vc[i:i + n] = torch.randn(n, page, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.randn(batch, 1, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    return q, kc, vc, torch.from_numpy(lens).to(dev), torch.from_numpy(table).to(dev), lens
+
+
+def decode_bytes(lens, hq, hkv, d, page):
+    """K and V rows of every cached token, q and o rows, block-table entries, the length."""
+    lens = np.asarray(lens, dtype=np.int64)
+    return int((2 * lens * hkv * d * 2).sum() + len(lens) * (2 * hq * d * 2) + (4 * ((lens + page - 1) // page)).sum() + 4 * len(lens))
+
+
+def time_steps(torch, fn, steps, warmup, barrier=None):
+    """W untimed + K timed calls; CUDA events on the current stream around the K calls."""
+    for _ in range(warmup):
+        fn()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1) / 1e3  # seconds for K steps
+
+
+def run_prefill(torch, low, ffi, dev, name, b, hq, hkv, s, d, steps, warmup, peaks, seed, scale_in=1.0, want_lse=True):
+    q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in)
+    o = torch.empty_like(q)
+    lse = torch.empty(b, hq, s, device=dev, dtype=torch.float32) if want_lse else None
+    scale = 1.0 / math.sqrt(d)
+
+    def step():
+        low.flash_attn(q, k, v, o, b, s, s, hq, hkv, d, 0, scale, None, None, lse)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches()
+    sec = time_steps(torch, step, steps, warmup)
+    flops = causal_flops(b, hq, s, s, d)
+    tf = flops * steps / sec / 1e12
+    peak = peaks["bf16_tflops"]
+    res = {
+        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+        "kernel_path": path, "launches_per_step": launches,
+        "config": {"workload": name, "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
+                   "causal": True, "lse": want_lse, "flops_per_step": flops,
+                   "l2_policy": "inputs larger than L2 (q+k+v+o = %d MiB)" % ((q.numel() * 2 + k.numel() * 4) * 2 // 2 ** 20 // 1)},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "traffic": None, "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
+                     "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
+    }
+    return res, (q, k, v, o, lse)
+
+
+def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool, steps, warmup, peaks, seed):
+    q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool, seed)
+    o = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    max_blocks = table_d.shape[1]
+
+    def step():
+        low.flash_attn_with_kvcache(q, kc, vc, o, table_d, lens_d, batch, 1, hq, hkv, d, page, max_blocks, scale)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches()
+    sec = time_steps(torch, step, steps, warmup)
+    nbytes = decode_bytes(lens, hq, hkv, d, page)
+    gbs = nbytes * steps / sec / 1e9
+    peak = peaks["hbm_gbs"]
+    res = {
+        "metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
+        "kernel_path": path, "launches_per_step": launches,
+        "config": {"workload": name, "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "page_size": page,
+                   "context": [int(lo), int(hi)], "tokens": int(lens.sum()), "pool_pages": int(kc.shape[0]),
+                   "bytes_per_step": nbytes, "l2_policy": "K/V touched per step (%d MiB) larger than L2" % (nbytes // 2 ** 20)},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth)",
+                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS},
+    }
+    return res, (q, kc, vc, o, lens_d, table_d)
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline (oracle port of luma-cpu's math path) — bounded sample of the primary workload
+# ------------------------------------------------------------------------------------------
+def cpu_baseline_prefill(b, hq, hkv, s, d, budget_s=12.0, seed=0):
+    from oracle import binding as ob
+    cores = ob.hardware_threads()
+    group = hq // hkv
+    rng = np.random.Generator(np.random.Philox(seed))
+
+    def make(nh_kv):
+        q = rng.standard_normal((1, s, nh_kv * group, d), dtype=np.float32)
+        k = rng.standard_normal((1, s, nh_kv, d), dtype=np.float32)
+        v = rng.standard_normal((1, s, nh_kv, d), dtype=np.float32)
+        return q, k, v
+
+    # probe with one KV head (and its query heads) of one batch element
+    q, k, v = make(1)
+    t0 = time.perf_counter()
+    ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
+    probe = time.perf_counter() - t0
+    nh = int(max(1, min(hkv, budget_s / max(probe, 1e-3))))
+    if nh > 1:
+        q, k, v = make(nh)
+        t0 = time.perf_counter()
+        ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
+        sec = time.perf_counter() - t0
+    else:
+        sec = probe
+    flops = causal_flops(1, nh * group, s, s, d)
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"1 of {b} batch elements x {nh * group} of {hq} query heads ({nh} KV heads), full S={s}, "
+                      f"f32 math path over the full key range, {sec:.2f} s; rate counts causal FLOPs only"}, sec
+
+
+def reference_arm(args):
+    """`--impl reference`: the CPU path, timed per step on a bounded sample of the primary workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    b, hq, hkv, s, d = 4, 32, 32, 2048, 128
+    from oracle import binding as ob
+    cores = ob.hardware_threads()
+    rng = np.random.Generator(np.random.Philox(0))
+    nh = 2
+    q = rng.standard_normal((1, s, nh, d), dtype=np.float32)
+    k = rng.standard_normal((1, s, nh, d), dtype=np.float32)
+    v = rng.standard_normal((1, s, nh, d), dtype=np.float32)
+    for _ in range(min(args.warmup, 2)):
+        ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
+    sec = time.perf_counter() - t0
+    flops = causal_flops(1, nh, s, s, d)
+    tf = flops * steps / sec / 1e12
+    sample = f"1 of {b} batch elements x {nh} of {hq} heads per step, full S={s}; f32 math path (oracle port of luma-cpu)"
+    print(json.dumps({
+        "impl": "reference", "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": sec / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "prefill_c2", "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
+                   "causal": True},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, help="run just one workload: prefill_c2, prefill_c3, decode_c4, prefill_c5, decode_c5")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--small", action="store_true", help="shrink every workload (for profiler captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small else args.warmup
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    from luma_b200 import ffi, low
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the measured path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks = load_peaks()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    sampler = ClockSampler(local_rank)
+    workloads = {}
+    only = args.only
+    K, W = args.steps, args.warmup
+
+    # ---- primary: BASELINE.json configs[1] --------------------------------------------------
+    b, hq, hkv, s, d = (4, 32, 32, 2048, 128) if not args.small else (1, 8, 8, 2048, 128)
+    if world == 1:
+        sampler.start()
+        primary, bufs = run_prefill(torch, low, ffi, dev, "prefill_c2", b, hq, hkv, s, d, K, W, peaks, seed=2)
+        clocks = sampler.stop()
+        q, k, v, o, lse = bufs
+        scaling_note = "single GPU"
+    else:
+        from luma_b200 import dist as fdist
+        q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed=2 + rank)
+        o_local = torch.empty_like(q)
+        lse = torch.empty(b, hq, s, device=dev, dtype=torch.float32)
+        gather = fdist.HeadAllGather(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
+        scale = 1.0 / math.sqrt(d)
+
+        def step():
+            low.flash_attn(q, k, v, o_local, b, s, s, hq, hkv, d, 0, scale, None, None, lse)
+            gather(o_local)
+
+        step()
+        path, launches = ffi.last_path(), ffi.last_launches() + gather.launches
+        sampler.start()
+        sec = time_steps(torch, step, K, W, barrier)
+        clocks = sampler.stop()
+        t = torch.tensor([sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+        flops = causal_flops(b, hq, s, s, d) * world
+        tf = flops * K / sec / 1e12
+        primary = {
+            "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / K * 1e3,
+            "kernel_path": path, "launches_per_step": launches,
+            "config": {"workload": "prefill_c2", "batch": b, "q_heads": hq * world, "kv_heads": hkv * world,
+                       "seq_len": s, "head_dim": d, "causal": True, "lse": True, "flops_per_step": flops,
+                       "parallelism": f"head-sharded x{world} (32 heads per GPU) + one all-gather of O along heads",
+                       "l2_policy": "inputs larger than L2"},
+            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / world / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included"},
+        }
+        o = o_local
+        scaling_note = "weak: 32 heads per GPU"
+
+    # ---- end to end through the host API with HOST buffers ------------------------------------
+    from luma_b200 import high
+    hq_h, hk_h, hv_h = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        qd = hq_h.to(dev, non_blocking=True)
+        kd = hk_h.to(dev, non_blocking=True)
+        vd = hv_h.to(dev, non_blocking=True)
+        od = high.flash_attn_func(qd, kd, vd, None, True, 0)
+        ho.copy_(od, non_blocking=True)
+
+    e2e_steps = max(3, min(K, 10))
+    sec_e2e = time_steps(torch, e2e_step, e2e_steps, 2, barrier)
+    if dist is not None:
+        t = torch.tensor([sec_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec_e2e = float(t.item())
+    e2e_flops = causal_flops(b, hq, s, s, d) * world
+    e2e = {"value": e2e_flops * e2e_steps / sec_e2e / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": int((q.numel() + k.numel() + v.numel()) * 2),
+           "d2h_bytes_per_step": int(q.numel() * 2), "steps": e2e_steps,
+           "note": "pinned host q/k/v -> device, flash_attn_func, output -> pinned host, per step, per GPU"}
+    del hq_h, hk_h, hv_h, ho
+
+    # ---- the other BASELINE.json configs ------------------------------------------------------
+    del q, k, v, o, lse
+    torch.cuda.empty_cache()
+    if world == 1 and not args.small:
+        extra_steps = max(3, min(K, 10))
+        if only in (None, "prefill_c3"):
+            workloads["prefill_c3"], _b = run_prefill(torch, low, ffi, dev, "prefill_c3", 2, 32, 8, 8192, 128,
+                                                      extra_steps, 3, peaks, seed=3, scale_in=0.5, want_lse=False)
+            del _b
+            torch.cuda.empty_cache()
+        if only in (None, "decode_c4"):
+            workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,
+                                                    40000, max(K, 20), 5, peaks, seed=4)
+            del _b
+            torch.cuda.empty_cache()
+
+    # ---- CPU baseline, rank 0, N == 1 only -----------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu and not args.small:
+        cpu, _ = cpu_baseline_prefill(4, 32, 32, 2048, 128)
+
+    if rank == 0:
+        line = {
+            "metric": primary["metric"], "value": primary["value"], "unit": primary["unit"],
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": primary["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": primary["config"], "roofline": primary["roofline"],
+            "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": int(primary["launches_per_step"]) * K, "kernel_path": primary["kernel_path"],
+            "scaling_note": scaling_note, "workloads": workloads,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,190 @@
+/*
+ * C ABI of the B200 (sm_100a) attention library, libflash_attn.
+ *
+ * The first ten symbols are exactly what luma's Rust crate `luma-flash-attn` binds in
+ * luma-flash-attn/src/api/ffi.rs:13-193 (status constants ffi.rs:6-11); a build of that crate
+ * that links this library instead of its own kernels/ *.cu needs no source change.
+ * Everything after the "additive" marker does not exist in the reference.
+ *
+ * Conventions shared by every entry point (reference: kernels/flash_attn_func.cu:267-328,
+ * kernels/flash_attn_varlen_func.cu:259-326, kernels/flash_attn_with_kvcache.cu:345-407):
+ *   - all tensors are dense row-major device buffers; element offsets are already applied;
+ *   - `o` is caller-allocated and may be uninitialised: every element is written, zeros for
+ *     rows that are invalid or see no key;
+ *   - `stream` is a CUstream / cudaStream_t (NULL = legacy default stream); launches are
+ *     asynchronous, nothing synchronises; execution-time faults surface at the caller's sync;
+ *   - the call makes the device that owns the pointers current for its own launches, so one
+ *     host thread per GPU can drive different devices;
+ *   - return value is a flash_attn_status; on failure flash_attn_last_error() holds a
+ *     NUL-terminated message (thread-local, at most 255 chars); every call clears it first;
+ *   - storage types f32 / f16 / bf16, arithmetic in f32, outputs rounded to nearest even;
+ *   - head_size must be 32, 64 or 128; q heads must be a multiple of kv heads (GQA).
+ * There is no CPU fallback: without a CUDA device every compute entry point returns
+ * FLASH_ATTN_ERR_CUDA.
+ */
+#ifndef LUMA_B200_FLASH_ATTN_H_
+#define LUMA_B200_FLASH_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* luma-flash-attn/kernels/common.cuh:17-24 == src/api/ffi.rs:6-11 */
+enum flash_attn_status {
+    FLASH_ATTN_OK = 0,
+    FLASH_ATTN_ERR_NULL_PTR = 1,
+    FLASH_ATTN_ERR_INVALID_SHAPE = 2,
+    FLASH_ATTN_ERR_INVALID_HEAD_SIZE = 3,
+    FLASH_ATTN_ERR_INVALID_START_POS = 4,
+    FLASH_ATTN_ERR_CUDA = 5
+};
+
+/* f16 / bf16 buffers are passed as raw 16-bit storage so that this header needs no CUDA include. */
+typedef uint16_t flash_attn_f16_t;
+typedef uint16_t flash_attn_bf16_t;
+
+/*
+ * Batched causal attention. Replaces flash_attn_{f32,f16,bf16}
+ * (ffi.rs:15-66; kernels/flash_attn_func.cu:312-328).
+ *   q, o : (batch, q_seq_len,  q_num_heads,  head_size)
+ *   k, v : (batch, kv_seq_len, kv_num_heads, head_size)
+ *   attn_mask : (batch, kv_seq_len) bytes, 1 = valid, 0 = padding, may be NULL. A masked key is
+ *               invisible; a query row whose own position start_pos+i is masked or >= kv_seq_len
+ *               outputs zeros (kernels/flash_attn_func.cu:74-84).
+ *   query row i sits at global position start_pos + i and sees keys j <= that.
+ * Check order: NULL q/k/v/o -> NULL_PTR; non-positive dims or Hq % Hkv != 0 -> INVALID_SHAPE;
+ * start_pos < 0 -> INVALID_START_POS; head_size not in {32,64,128} -> INVALID_HEAD_SIZE.
+ */
+int flash_attn_f32(const float* q, const float* k, const float* v, float* o,
+                   int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                   int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+int flash_attn_f16(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                   flash_attn_f16_t* o,
+                   int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                   int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+int flash_attn_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                    flash_attn_bf16_t* o,
+                    int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                    int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+
+/*
+ * Packed variable-length causal attention, bottom-right aligned, K/V contiguous or paged.
+ * Replaces flash_attn_varlen_{f32,f16,bf16} (ffi.rs:68-132;
+ * kernels/flash_attn_varlen_func.cu:308-326).
+ *   q, o : (total_q, q_heads, head_size)
+ *   k, v : (total_kv, kv_heads, head_size), or when k_paged != 0 a cache
+ *          (num_blocks, block_size, kv_heads, head_size) addressed through
+ *          block_tables (num_seqs, max_blocks)
+ *   cu_seqlens_q / cu_seqlens_k : (num_seqs + 1) i32 prefix sums; with a paged cache only the
+ *          differences of cu_seqlens_k are used (the per-sequence cached length).
+ * Check order: NULL q/o/cu_seqlens -> NULL_PTR; NULL k/v (or block_tables when paged) -> NULL_PTR;
+ * num_seqs/heads <= 0, Hq % Hkv, head_size not in {32,64,128} -> INVALID_SHAPE;
+ * max_seqlen_q/max_seqlen_k/block_size <= 0 -> INVALID_SHAPE.
+ */
+int flash_attn_varlen_f32(const float* q, const float* k, const float* v, float* o,
+                          const int* cu_seqlens_q, const int* cu_seqlens_k, const int* block_tables,
+                          int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads, int kv_heads,
+                          int head_size, int block_size, int max_blocks, int k_paged, float scale,
+                          void* stream);
+int flash_attn_varlen_f16(const flash_attn_f16_t* q, const flash_attn_f16_t* k,
+                          const flash_attn_f16_t* v, flash_attn_f16_t* o,
+                          const int* cu_seqlens_q, const int* cu_seqlens_k, const int* block_tables,
+                          int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads, int kv_heads,
+                          int head_size, int block_size, int max_blocks, int k_paged, float scale,
+                          void* stream);
+int flash_attn_varlen_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k,
+                           const flash_attn_bf16_t* v, flash_attn_bf16_t* o,
+                           const int* cu_seqlens_q, const int* cu_seqlens_k, const int* block_tables,
+                           int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads, int kv_heads,
+                           int head_size, int block_size, int max_blocks, int k_paged, float scale,
+                           void* stream);
+
+/*
+ * Attention over a paged KV cache: q_seq_len == 1 is single-token decode, > 1 is chunked
+ * prefill (bottom-right causal: row i sits at context_lens[s] - q_seq_len + i).
+ * Replaces flash_attn_with_kvcache_{f32,f16,bf16} (ffi.rs:134-189;
+ * kernels/flash_attn_with_kvcache.cu:390-407).
+ *   q, o : (num_seqs, q_seq_len, q_heads, head_size)
+ *   k_cache, v_cache : (num_blocks, block_size, kv_heads, head_size)
+ *   block_tables : (num_seqs, max_blocks) i32, logical block -> physical block
+ *   context_lens : (num_seqs) i32, total cached length including the q tokens
+ * Token j of sequence s lives at slot block_tables[s*max_blocks + j/block_size]*block_size +
+ * j%block_size (kernels/common.cuh:89-108); element offsets are 64-bit.
+ * Check order: any NULL -> NULL_PTR; num_seqs/heads <= 0, Hq % Hkv, head_size not in {32,64,128},
+ * q_seq_len <= 0, block_size <= 0 -> INVALID_SHAPE.
+ * The decode path keeps a per-device, per-stream split-K workspace inside the library; it is
+ * grown with cudaMalloc on the first call that needs more (that call synchronises the device).
+ */
+int flash_attn_with_kvcache_f32(const float* q, const float* k_cache, const float* v_cache, float* o,
+                                const int* block_tables, const int* context_lens,
+                                int num_seqs, int q_seq_len, int q_heads, int kv_heads, int head_size,
+                                int block_size, int max_blocks, float scale, void* stream);
+int flash_attn_with_kvcache_f16(const flash_attn_f16_t* q, const flash_attn_f16_t* k_cache,
+                                const flash_attn_f16_t* v_cache, flash_attn_f16_t* o,
+                                const int* block_tables, const int* context_lens,
+                                int num_seqs, int q_seq_len, int q_heads, int kv_heads, int head_size,
+                                int block_size, int max_blocks, float scale, void* stream);
+int flash_attn_with_kvcache_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k_cache,
+                                 const flash_attn_bf16_t* v_cache, flash_attn_bf16_t* o,
+                                 const int* block_tables, const int* context_lens,
+                                 int num_seqs, int q_seq_len, int q_heads, int kv_heads, int head_size,
+                                 int block_size, int max_blocks, float scale, void* stream);
+
+/* Thread-local message of the last failing call on this thread; never NULL
+ * (ffi.rs:191-192; kernels/flash_attn_func.cu:308-310). */
+const char* flash_attn_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Additive symbols (no counterpart in the reference's ffi.rs).
+ * ------------------------------------------------------------------------------------------ */
+
+/*
+ * flash_attn_<T> plus an fp32 log-sum-exp output: lse is (batch, q_num_heads, q_seq_len),
+ * natural log of the sum of exp(scale * q.k) over the visible keys; -inf for rows that output
+ * zeros. lse may be NULL (then identical to flash_attn_<T>). No counterpart in the reference.
+ */
+int flash_attn_f32_lse(const float* q, const float* k, const float* v, float* o, float* lse,
+                       int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                       int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+int flash_attn_f16_lse(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                       flash_attn_f16_t* o, float* lse,
+                       int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                       int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+int flash_attn_bf16_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                        flash_attn_bf16_t* o, float* lse,
+                        int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                        int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
+
+/*
+ * Runs the device-side block_slot arithmetic of the paged kernels and writes, for every sequence
+ * s and token j < context_lens[s], the physical token slot to out_slots[offsets[s] + j]
+ * (offsets = exclusive prefix sum of context_lens, supplied by the caller, num_seqs entries).
+ * Exists so that page indexing can be checked bit for bit against a host walk of the table.
+ * No counterpart in the reference.
+ */
+int flash_attn_debug_block_slots(const int* block_tables, const int* context_lens, const int* offsets,
+                                 int num_seqs, int block_size, int max_blocks, int* out_slots,
+                                 void* stream);
+
+/*
+ * Tuning and introspection. No counterpart in the reference.
+ *   flash_attn_version        : library version string.
+ *   flash_attn_last_path      : name of the kernel family the last successful call on this
+ *                               thread dispatched to ("prefill_tcgen05", "decode_splitk", "tile_simt").
+ *   flash_attn_last_launches  : number of kernels that call launched.
+ *   flash_attn_set_option     : named integer knobs (returns 0 if the name is known):
+ *       "force_generic"       1 = route everything through the SIMT tile kernel
+ *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
+ */
+const char* flash_attn_version(void);
+const char* flash_attn_last_path(void);
+int flash_attn_last_launches(void);
+int flash_attn_set_option(const char* name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LUMA_B200_FLASH_ATTN_H_ */

@@ -1,0 +1,380 @@
+// extern "C" entry points of libflash_attn: argument validation in the reference's order with the
+// reference's status codes, thread-local last-error string, device selection, and dispatch to the
+// kernel families (tcgen05 prefill, split-K paged decode, SIMT tile kernel for everything else).
+//
+// Validation order and codes follow
+//   luma-flash-attn/kernels/flash_attn_func.cu:267-304
+//   luma-flash-attn/kernels/flash_attn_varlen_func.cu:243-304
+//   luma-flash-attn/kernels/flash_attn_with_kvcache.cu:313-386
+#include <cstdarg>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fa {
+
+namespace {
+thread_local char g_last_error[256] = {0};
+thread_local const char* g_last_path = "";
+thread_local int g_last_launches = 0;
+int g_force_generic = 0;
+int g_decode_chunk = 0;
+}  // namespace
+
+void set_last_error(const char* msg) { std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
+
+void set_last_errorf(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+}
+
+void note_path(const char* name, int launches) {
+    g_last_path = name;
+    g_last_launches = launches;
+}
+
+int get_option_force_generic() { return g_force_generic; }
+int get_option_decode_chunk() { return g_decode_chunk; }
+
+int check_launch(const char* what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        set_last_errorf("%s: %s", what, cudaGetErrorString(err));
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    return FLASH_ATTN_OK;
+}
+
+// ---- decode split-K workspace: one buffer per (device, stream) ---------------------------
+namespace {
+struct WsEntry {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+std::mutex g_ws_mutex;
+std::map<std::pair<int, cudaStream_t>, WsEntry> g_ws;
+}  // namespace
+
+void* decode_workspace(cudaStream_t stream, size_t bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    WsEntry& e = g_ws[{dev, stream}];
+    if (e.bytes >= bytes && e.ptr != nullptr) return e.ptr;
+    if (e.ptr != nullptr) {
+        // cudaFree waits for work that may still read the old buffer
+        cudaFree(e.ptr);
+        e.ptr = nullptr;
+        e.bytes = 0;
+    }
+    size_t want = bytes + bytes / 4;
+    if (want < (size_t(1) << 20)) want = size_t(1) << 20;
+    void* ptr = nullptr;
+    if (cudaMalloc(&ptr, want) != cudaSuccess) {
+        cudaGetLastError();
+        want = bytes;
+        if (cudaMalloc(&ptr, want) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+    }
+    e.ptr = ptr;
+    e.bytes = want;
+    return ptr;
+}
+
+namespace {
+
+// Makes the device that owns `ptr` current for the lifetime of the guard.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    bool ok = true;
+    explicit DeviceGuard(const void* ptr) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+            cudaGetLastError();
+            return;  // not a CUDA pointer we can classify: launch on the current device
+        }
+        if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) return;
+        if (cudaGetDevice(&prev) != cudaSuccess) {
+            ok = false;
+            return;
+        }
+        if (attr.device != prev) {
+            ok = cudaSetDevice(attr.device) == cudaSuccess;
+            switched = ok;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+bool have_device() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        set_last_error("flash_attn: no CUDA device available (this library has no CPU fallback)");
+        return false;
+    }
+    return true;
+}
+
+int dispatch(const AttnParams& p, cudaStream_t stream) {
+    if (!have_device()) return FLASH_ATTN_ERR_CUDA;
+    DeviceGuard guard(p.q);
+    if (!guard.ok) {
+        set_last_error("flash_attn: could not select the device that owns q");
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    if (!g_force_generic) {
+        int rc = launch_decode_splitk(p, stream);
+        if (rc >= 0) return rc;
+        rc = launch_prefill_tcgen05(p, stream);
+        if (rc >= 0) return rc;
+    }
+    return launch_tile_simt(p, stream);
+}
+
+bool head_size_ok(int h) { return h == 32 || h == 64 || h == 128; }
+
+int batch_impl(int dtype, const void* q, const void* k, const void* v, void* o, float* lse,
+               int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+               int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream) {
+    g_last_error[0] = '\0';
+    cudaGetLastError();  // swallow a sticky error left by someone else, as the reference does
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) {
+        set_last_error("flash_attn: q/k/v/o must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (batch <= 0 || q_seq_len <= 0 || kv_seq_len <= 0 || q_num_heads <= 0 || kv_num_heads <= 0) {
+        set_last_error("flash_attn: shape parameters must be positive");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_num_heads % kv_num_heads != 0) {
+        set_last_error("flash_attn: q_num_heads must be a multiple of kv_num_heads (GQA)");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (start_pos < 0) {
+        set_last_error("flash_attn: start_pos must be >= 0");
+        return FLASH_ATTN_ERR_INVALID_START_POS;
+    }
+    if (!head_size_ok(head_size)) {
+        set_last_error("flash_attn: unsupported head_size (only 32/64/128)");
+        return FLASH_ATTN_ERR_INVALID_HEAD_SIZE;
+    }
+    AttnParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
+    p.mask = attn_mask;
+    p.mode = MODE_BATCH;
+    p.dtype = dtype;
+    p.num_seqs = batch;
+    p.q_seq_len = q_seq_len;
+    p.kv_seq_len = kv_seq_len;
+    p.q_heads = q_num_heads;
+    p.kv_heads = kv_num_heads;
+    p.head_size = head_size;
+    p.start_pos = start_pos;
+    p.block_size = 1;
+    p.scale = scale;
+    return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
+                const int* cu_seqlens_q, const int* cu_seqlens_k, const int* block_tables,
+                int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads, int kv_heads,
+                int head_size, int block_size, int max_blocks, int k_paged, float scale, void* stream) {
+    g_last_error[0] = '\0';
+    cudaGetLastError();
+    if (q == nullptr || o == nullptr || cu_seqlens_q == nullptr || cu_seqlens_k == nullptr) {
+        set_last_error("flash_attn_varlen: q/o/cu_seqlens must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (k == nullptr || v == nullptr || (k_paged && block_tables == nullptr)) {
+        set_last_error("flash_attn_varlen: k/v (and block_tables when paged) must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (num_seqs <= 0 || q_heads <= 0 || kv_heads <= 0) {
+        set_last_error("flash_attn_varlen: num_seqs/q_heads/kv_heads must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_heads % kv_heads != 0) {
+        set_last_error("flash_attn_varlen: q_heads must be a multiple of kv_heads (GQA)");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (!head_size_ok(head_size)) {
+        set_last_error("flash_attn_varlen: head_size must be 32/64/128");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (max_seqlen_q <= 0 || max_seqlen_k <= 0 || block_size <= 0) {
+        set_last_error("flash_attn_varlen: max_seqlen_q/k and block_size must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    AttnParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o;
+    p.cu_q = cu_seqlens_q;
+    p.cu_k = cu_seqlens_k;
+    p.block_tables = k_paged ? block_tables : nullptr;
+    p.mode = MODE_VARLEN;
+    p.dtype = dtype;
+    p.num_seqs = num_seqs;
+    p.q_seq_len = max_seqlen_q;
+    p.kv_seq_len = max_seqlen_k;
+    p.q_heads = q_heads;
+    p.kv_heads = kv_heads;
+    p.head_size = head_size;
+    p.block_size = block_size;
+    p.max_blocks = max_blocks;
+    p.paged = k_paged ? 1 : 0;
+    p.scale = scale;
+    return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int kvcache_impl(int dtype, const void* q, const void* k_cache, const void* v_cache, void* o,
+                 const int* block_tables, const int* context_lens, int num_seqs, int q_seq_len,
+                 int q_heads, int kv_heads, int head_size, int block_size, int max_blocks,
+                 float scale, void* stream) {
+    g_last_error[0] = '\0';
+    cudaGetLastError();
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || o == nullptr ||
+        block_tables == nullptr || context_lens == nullptr) {
+        set_last_error("flash_attn_with_kvcache: null pointer argument");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (num_seqs <= 0 || q_heads <= 0 || kv_heads <= 0) {
+        set_last_error("flash_attn_with_kvcache: num_seqs/q_heads/kv_heads must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_heads % kv_heads != 0) {
+        set_last_error("flash_attn_with_kvcache: q_heads must be a multiple of kv_heads (GQA)");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (!head_size_ok(head_size)) {
+        set_last_error("flash_attn_with_kvcache: head_size must be 32/64/128");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_seq_len <= 0) {
+        set_last_error("flash_attn_with_kvcache: q_seq_len must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (block_size <= 0) {
+        set_last_error("flash_attn_with_kvcache: block_size must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    AttnParams p{};
+    p.q = q; p.k = k_cache; p.v = v_cache; p.o = o;
+    p.block_tables = block_tables;
+    p.context_lens = context_lens;
+    p.mode = MODE_KVCACHE;
+    p.dtype = dtype;
+    p.num_seqs = num_seqs;
+    p.q_seq_len = q_seq_len;
+    p.kv_seq_len = (max_blocks > 0 && (long long)max_blocks * block_size < 0x7fffffffLL)
+                       ? max_blocks * block_size : 0x7fffffff;
+    p.q_heads = q_heads;
+    p.kv_heads = kv_heads;
+    p.head_size = head_size;
+    p.block_size = block_size;
+    p.max_blocks = max_blocks;
+    p.paged = 1;
+    p.scale = scale;
+    return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace fa
+
+extern "C" {
+
+const char* flash_attn_last_error(void) { return fa::g_last_error; }
+const char* flash_attn_version(void) { return "luma-b200-flash-attn 0.1.0 (sm_100a)"; }
+const char* flash_attn_last_path(void) { return fa::g_last_path; }
+int flash_attn_last_launches(void) { return fa::g_last_launches; }
+
+int flash_attn_set_option(const char* name, int value) {
+    if (name == nullptr) return 1;
+    if (std::strcmp(name, "force_generic") == 0) {
+        fa::g_force_generic = value;
+        return 0;
+    }
+    if (std::strcmp(name, "decode_chunk_tokens") == 0) {
+        fa::g_decode_chunk = value;
+        return 0;
+    }
+    return 1;
+}
+
+#define FA_DEFINE_BATCH(NAME, CTYPE, DT)                                                            \
+    int NAME(const CTYPE* q, const CTYPE* k, const CTYPE* v, CTYPE* o, int batch, int q_seq_len,    \
+             int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size, int start_pos,       \
+             float scale, const uint8_t* attn_mask, void* stream) {                                 \
+        return fa::batch_impl(DT, q, k, v, o, nullptr, batch, q_seq_len, kv_seq_len, q_num_heads,   \
+                              kv_num_heads, head_size, start_pos, scale, attn_mask, stream);        \
+    }                                                                                               \
+    int NAME##_lse(const CTYPE* q, const CTYPE* k, const CTYPE* v, CTYPE* o, float* lse, int batch, \
+                   int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size, \
+                   int start_pos, float scale, const uint8_t* attn_mask, void* stream) {            \
+        return fa::batch_impl(DT, q, k, v, o, lse, batch, q_seq_len, kv_seq_len, q_num_heads,       \
+                              kv_num_heads, head_size, start_pos, scale, attn_mask, stream);        \
+    }
+
+FA_DEFINE_BATCH(flash_attn_f32, float, fa::DT_F32)
+FA_DEFINE_BATCH(flash_attn_f16, flash_attn_f16_t, fa::DT_F16)
+FA_DEFINE_BATCH(flash_attn_bf16, flash_attn_bf16_t, fa::DT_BF16)
+#undef FA_DEFINE_BATCH
+
+#define FA_DEFINE_VARLEN(NAME, CTYPE, DT)                                                           \
+    int NAME(const CTYPE* q, const CTYPE* k, const CTYPE* v, CTYPE* o, const int* cu_seqlens_q,     \
+             const int* cu_seqlens_k, const int* block_tables, int num_seqs, int max_seqlen_q,      \
+             int max_seqlen_k, int q_heads, int kv_heads, int head_size, int block_size,            \
+             int max_blocks, int k_paged, float scale, void* stream) {                              \
+        return fa::varlen_impl(DT, q, k, v, o, cu_seqlens_q, cu_seqlens_k, block_tables, num_seqs,  \
+                               max_seqlen_q, max_seqlen_k, q_heads, kv_heads, head_size,            \
+                               block_size, max_blocks, k_paged, scale, stream);                     \
+    }
+
+FA_DEFINE_VARLEN(flash_attn_varlen_f32, float, fa::DT_F32)
+FA_DEFINE_VARLEN(flash_attn_varlen_f16, flash_attn_f16_t, fa::DT_F16)
+FA_DEFINE_VARLEN(flash_attn_varlen_bf16, flash_attn_bf16_t, fa::DT_BF16)
+#undef FA_DEFINE_VARLEN
+
+#define FA_DEFINE_KVCACHE(NAME, CTYPE, DT)                                                          \
+    int NAME(const CTYPE* q, const CTYPE* k_cache, const CTYPE* v_cache, CTYPE* o,                  \
+             const int* block_tables, const int* context_lens, int num_seqs, int q_seq_len,         \
+             int q_heads, int kv_heads, int head_size, int block_size, int max_blocks, float scale, \
+             void* stream) {                                                                        \
+        return fa::kvcache_impl(DT, q, k_cache, v_cache, o, block_tables, context_lens, num_seqs,   \
+                                q_seq_len, q_heads, kv_heads, head_size, block_size, max_blocks,    \
+                                scale, stream);                                                     \
+    }
+
+FA_DEFINE_KVCACHE(flash_attn_with_kvcache_f32, float, fa::DT_F32)
+FA_DEFINE_KVCACHE(flash_attn_with_kvcache_f16, flash_attn_f16_t, fa::DT_F16)
+FA_DEFINE_KVCACHE(flash_attn_with_kvcache_bf16, flash_attn_bf16_t, fa::DT_BF16)
+#undef FA_DEFINE_KVCACHE
+
+int flash_attn_debug_block_slots(const int* block_tables, const int* context_lens, const int* offsets,
+                                 int num_seqs, int block_size, int max_blocks, int* out_slots,
+                                 void* stream) {
+    fa::g_last_error[0] = '\0';
+    cudaGetLastError();
+    if (!block_tables || !context_lens || !offsets || !out_slots) {
+        fa::set_last_error("flash_attn_debug_block_slots: null pointer argument");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (num_seqs <= 0 || block_size <= 0 || max_blocks <= 0) {
+        fa::set_last_error("flash_attn_debug_block_slots: num_seqs/block_size/max_blocks must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (!fa::have_device()) return FLASH_ATTN_ERR_CUDA;
+    fa::DeviceGuard guard(block_tables);
+    return fa::launch_debug_block_slots(block_tables, context_lens, offsets, num_seqs, block_size,
+                                        max_blocks, out_slots, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

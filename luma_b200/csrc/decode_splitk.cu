@@ -1,0 +1,470 @@
+// Paged-KV single-token decode for f16/bf16 storage, head_size 64 or 128.
+//
+// Replaces flash_attn_decode_kernel (luma-flash-attn/kernels/flash_attn_with_kvcache.cu:22-116;
+// launch :123-145), which walks the context one token at a time with one warp per query head and
+// re-reads K/V once per query head of a GQA group.
+//
+// Here the path is HBM-bound by construction:
+//   * work item = (chunk of the context, KV head, sequence); a CTA reads each K/V row of its chunk
+//     exactly once and serves every query head of the GQA group from it;
+//   * rows are gathered through the block table with 16-byte cp.async copies into a per-warp ring
+//     of shared-memory stages (3 tiles of 16 tokens in flight per warp, 2 CTAs per SM), no
+//     CTA-wide barrier inside the loop;
+//   * Q.K^T and P.V run on tensor cores (mma.sync m16n8k16, f32 accumulate) with the group's
+//     query heads as the 16-row M dimension — at 8 query heads per KV head scalar FMA could not
+//     keep up with the memory system;
+//   * split-K over the context: every chunk writes an unnormalised f32 partial (acc, m, l) to a
+//     workspace and a second kernel merges the chunks of a sequence with log-sum-exp weights.
+// Token -> slot arithmetic is block_slot() from common.cuh (reference: kernels/common.cuh:89-108).
+#include "common.cuh"
+
+namespace fa {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTile = 16;    // tokens per tile (one mma K step for P.V, two N blocks for Q.K^T)
+constexpr int kStages = 3;   // tiles in flight per warp
+constexpr int kMaxHeads = 16;  // query heads served per CTA (M of the mma)
+
+struct DecodeArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    const int* block_tables;
+    const int* context_lens;
+    float* ws_acc;   // (num_seqs, q_heads, max_splits, D) f32, unnormalised
+    float2* ws_ml;   // (num_seqs, q_heads, max_splits) {m (log2 domain), l}
+    int num_seqs, q_heads, kv_heads, block_size, max_blocks;
+    int chunk;       // tokens per work item, multiple of kWarps * kTile
+    int max_splits;
+    int head_blocks; // ceil(group / kMaxHeads)
+    float scale_log2;  // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned saddr = (unsigned)__cvta_generic_to_shared(smem);
+    const int src_bytes = valid ? 16 : 0;  // 0 -> the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                            const void* smem) {
+    const unsigned saddr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(saddr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                                  const void* smem) {
+    const unsigned saddr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(saddr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1);
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], const unsigned (&a)[4], unsigned b0,
+                                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&d)[4], const unsigned (&a)[4], unsigned b0,
+                                                  unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ unsigned pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&t);
+}
+template <>
+__device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&t);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared memory of one CTA:
+//   ring : kWarps x kStages x {K tile, V tile}, each tile kTile rows of D elements, 16-byte chunks
+//          XOR-swizzled by (row & 7) so ldmatrix reads are bank-conflict free
+//   after the loop the same bytes hold the per-warp partials for the cross-warp merge.
+template <int D>
+struct Smem {
+    static constexpr int kRowBytes = D * 2;
+    static constexpr int kTileBytes = kTile * kRowBytes;
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kWarpBytes = kStages * kStageBytes;
+    static constexpr int kRingBytes = kWarps * kWarpBytes;
+    static constexpr int kMergeBytes = kWarps * kMaxHeads * (D + 2) * 4;
+    static constexpr int kBytes = kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const DecodeArgs a) {
+    using S = Smem<D>;
+    constexpr int kChunksPerRow = D / 8;          // 16-byte chunks per K/V row
+    constexpr int kCopiesPerLane = kChunksPerRow / 2;  // a lane copies half a row of K and of V
+    constexpr int kKSteps = D / 16;
+    constexpr int kDBlocks = D / 8;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;   // mma row group
+    const int c4 = lane & 3;
+
+    const int split = blockIdx.x;
+    const int kvh = blockIdx.y / a.head_blocks;
+    const int hb = blockIdx.y - kvh * a.head_blocks;
+    const int s = blockIdx.z;
+
+    const int L = a.context_lens[s];
+    const int chunk_begin = split * a.chunk;
+    if (chunk_begin >= L) return;  // nothing cached here (L <= 0 included): the merge kernel writes zeros
+    const int chunk_end = min(L, chunk_begin + a.chunk);
+
+    const int group = a.q_heads / a.kv_heads;
+    const int head0 = kvh * group + hb * kMaxHeads;            // first query head of this CTA
+    const int nheads = min(kMaxHeads, group - hb * kMaxHeads);  // query heads served
+
+    const T* __restrict__ qg = static_cast<const T*>(a.q);
+    const T* __restrict__ kg = static_cast<const T*>(a.k);
+    const T* __restrict__ vg = static_cast<const T*>(a.v);
+    const long long kv_pitch = (long long)a.kv_heads * D;
+
+    // Q fragments of the A operand, straight from global: row g and g+8 of the head block.
+    unsigned qa[kKSteps][4];
+    {
+        const unsigned* q0 = reinterpret_cast<const unsigned*>(qg + ((long long)s * a.q_heads + head0 + g) * D);
+        const unsigned* q1 = reinterpret_cast<const unsigned*>(qg + ((long long)s * a.q_heads + head0 + g + 8) * D);
+        const bool v0 = g < nheads, v1 = g + 8 < nheads;
+#pragma unroll
+        for (int kk = 0; kk < kKSteps; ++kk) {
+            qa[kk][0] = v0 ? q0[kk * 8 + c4] : 0u;
+            qa[kk][1] = v1 ? q1[kk * 8 + c4] : 0u;
+            qa[kk][2] = v0 ? q0[kk * 8 + 4 + c4] : 0u;
+            qa[kk][3] = v1 ? q1[kk * 8 + 4 + c4] : 0u;
+        }
+    }
+
+    float acc[kDBlocks][4];
+#pragma unroll
+    for (int n = 0; n < kDBlocks; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY;  // running max of rows g and g+8 (log2 domain)
+    float l0 = 0.0f, l1 = 0.0f;            // this lane's share of the running sums
+
+    unsigned char* ring = smem_raw + warp * S::kWarpBytes;
+    const int n_tiles = (chunk_end - chunk_begin + kTile - 1) / kTile;   // tiles in the chunk
+    const int my_tiles = (n_tiles - warp + kWarps - 1) / kWarps;         // tiles warp takes: warp, warp+4, ...
+
+    // one lane moves half a row (8 or 4 chunks) of K and of V for token row lane/2
+    const int cp_row = lane >> 1;
+    const int cp_half = lane & 1;
+    auto issue = [&](int it) {
+        if (it < my_tiles) {
+            const int tile = warp + it * kWarps;
+            const int j = chunk_begin + tile * kTile + cp_row;
+            const bool valid = j < chunk_end;
+            long long off = 0;
+            if (valid) {
+                const int slot = block_slot(a.block_tables, s, a.max_blocks, j, a.block_size);
+                off = (long long)slot * kv_pitch + (long long)kvh * D;
+            }
+            unsigned char* kst = ring + (it % kStages) * S::kStageBytes;
+            unsigned char* vst = kst + S::kTileBytes;
+            const T* ksrc = kg + off;
+            const T* vsrc = vg + off;
+#pragma unroll
+            for (int i = 0; i < kCopiesPerLane; ++i) {
+                const int ch = cp_half * kCopiesPerLane + i;
+                const int dst = cp_row * S::kRowBytes + ((ch ^ (cp_row & 7)) << 4);
+                cp_async_16(kst + dst, ksrc + ch * 8, valid);
+                cp_async_16(vst + dst, vsrc + ch * 8, valid);
+            }
+        }
+        cp_async_commit();  // committed even when empty so that group counting stays uniform
+    };
+
+#pragma unroll
+    for (int it = 0; it < kStages - 1; ++it) issue(it);
+
+    for (int it = 0; it < my_tiles; ++it) {
+        issue(it + kStages - 1);
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+
+        const unsigned char* kst = ring + (it % kStages) * S::kStageBytes;
+        const unsigned char* vst = kst + S::kTileBytes;
+        const int tile_tok0 = chunk_begin + (warp + it * kWarps) * kTile;
+
+        // S = Q K^T : 16 heads x 16 tokens as two N blocks of 8 tokens
+        float sc[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.0f;
+        {
+            const int mi = lane >> 3;                    // which 8x8 matrix this lane addresses
+            const int tok = ((mi >> 1) << 3) + (lane & 7);  // token row
+#pragma unroll
+            for (int kk = 0; kk < kKSteps; ++kk) {
+                const int ch = 2 * kk + (mi & 1);
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, kst + tok * S::kRowBytes + ((ch ^ (tok & 7)) << 4));
+                mma_16816<T>(sc[0], qa[kk], b0, b1);
+                mma_16816<T>(sc[1], qa[kk], b2, b3);
+            }
+        }
+
+        // scale, mask the tail of the chunk, online softmax over this tile's 16 tokens
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = tile_tok0 + nb * 8 + 2 * c4 + e;
+                const bool vis = j < chunk_end;
+                sc[nb][e] = vis ? sc[nb][e] * a.scale_log2 : -INFINITY;
+                sc[nb][2 + e] = vis ? sc[nb][2 + e] * a.scale_log2 : -INFINITY;
+                tmax0 = fmaxf(tmax0, sc[nb][e]);
+                tmax1 = fmaxf(tmax1, sc[nb][2 + e]);
+            }
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        // every tile inside the chunk has at least its first token visible, so the maxima are finite
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
+        const float alpha0 = fast_exp2(m0 - mn0), alpha1 = fast_exp2(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        float ps0 = 0.0f, ps1 = 0.0f;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                sc[nb][e] = fast_exp2(sc[nb][e] - mn0);
+                sc[nb][2 + e] = fast_exp2(sc[nb][2 + e] - mn1);
+                ps0 += sc[nb][e];
+                ps1 += sc[nb][2 + e];
+            }
+        }
+        l0 = l0 * alpha0 + ps0;
+        l1 = l1 * alpha1 + ps1;
+#pragma unroll
+        for (int n = 0; n < kDBlocks; ++n) {
+            acc[n][0] *= alpha0;
+            acc[n][1] *= alpha0;
+            acc[n][2] *= alpha1;
+            acc[n][3] *= alpha1;
+        }
+
+        // O += P V : P (16 heads x 16 tokens) re-used from the accumulator layout as the A operand
+        unsigned pa[4];
+        pa[0] = pack2<T>(sc[0][0], sc[0][1]);
+        pa[1] = pack2<T>(sc[0][2], sc[0][3]);
+        pa[2] = pack2<T>(sc[1][0], sc[1][1]);
+        pa[3] = pack2<T>(sc[1][2], sc[1][3]);
+        {
+            const int mi = lane >> 3;
+            const int tok = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int n = 0; n < kDBlocks; n += 2) {
+                const int ch = n + (mi >> 1);
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, vst + tok * S::kRowBytes + ((ch ^ (tok & 7)) << 4));
+                mma_16816<T>(acc[n], pa, b0, b1);
+                mma_16816<T>(acc[n + 1], pa, b2, b3);
+            }
+        }
+        __syncwarp();  // the stage may be refilled by the next issue()
+    }
+    cp_async_wait<0>();
+
+    // row sums: fold the four lanes that share a row
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // cross-warp merge through shared memory (the ring is dead now)
+    __syncthreads();
+    float* merge = reinterpret_cast<float*>(smem_raw);
+    float* macc = merge + warp * kMaxHeads * (D + 2);  // [head][D + 2]: acc, m, l
+#pragma unroll
+    for (int n = 0; n < kDBlocks; ++n) {
+        const int d = n * 8 + 2 * c4;
+        macc[g * (D + 2) + d] = acc[n][0];
+        macc[g * (D + 2) + d + 1] = acc[n][1];
+        macc[(g + 8) * (D + 2) + d] = acc[n][2];
+        macc[(g + 8) * (D + 2) + d + 1] = acc[n][3];
+    }
+    if (c4 == 0) {
+        macc[g * (D + 2) + D] = m0;
+        macc[g * (D + 2) + D + 1] = l0;
+        macc[(g + 8) * (D + 2) + D] = m1;
+        macc[(g + 8) * (D + 2) + D + 1] = l1;
+    }
+    __syncthreads();
+
+    for (int idx = threadIdx.x; idx < nheads * D; idx += kThreads) {
+        const int hh = idx / D;
+        const int d = idx - hh * D;
+        float mw[kWarps];
+        float mstar = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            mw[w] = merge[(w * kMaxHeads + hh) * (D + 2) + D];
+            mstar = fmaxf(mstar, mw[w]);
+        }
+        float o = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float wgt = (mw[w] == -INFINITY) ? 0.0f : fast_exp2(mw[w] - mstar);
+            o += wgt * merge[(w * kMaxHeads + hh) * (D + 2) + d];
+            l += wgt * merge[(w * kMaxHeads + hh) * (D + 2) + D + 1];
+        }
+        const long long row = ((long long)s * a.q_heads + head0 + hh) * a.max_splits + split;
+        a.ws_acc[row * D + d] = o;
+        if (d == 0) a.ws_ml[row] = make_float2(mstar, l);
+    }
+}
+
+// Merges the split-K partials of one (sequence, query head) and writes the output row.
+template <typename T, int D>
+__global__ void __launch_bounds__(D) decode_merge_kernel(const float* __restrict__ ws_acc,
+                                                         const float2* __restrict__ ws_ml,
+                                                         const int* __restrict__ context_lens,
+                                                         T* __restrict__ o, int q_heads, int chunk,
+                                                         int max_splits) {
+    const int h = blockIdx.x;
+    const int s = blockIdx.y;
+    const int d = threadIdx.x;
+    const int L = context_lens[s];
+    const int n = L > 0 ? min(max_splits, (L + chunk - 1) / chunk) : 0;
+    const long long row0 = ((long long)s * q_heads + h) * max_splits;
+    float mstar = -INFINITY;
+    for (int i = 0; i < n; ++i) mstar = fmaxf(mstar, ws_ml[row0 + i].x);
+    float acc = 0.0f, l = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        const float2 ml = ws_ml[row0 + i];
+        const float w = (ml.x == -INFINITY) ? 0.0f : fast_exp2(ml.x - mstar);
+        acc += w * ws_acc[(row0 + i) * D + d];
+        l += w * ml.y;
+    }
+    // reference: inv = l > 0 ? 1/l : 0 (flash_attn_with_kvcache.cu:109)
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    o[((long long)s * q_heads + h) * D + d] = from_f32<T>(acc * inv);
+}
+
+template <typename T, int D>
+int launch_typed(const AttnParams& p, cudaStream_t stream) {
+    using S = Smem<D>;
+    const int group = p.q_heads / p.kv_heads;
+    const int head_blocks = (group + kMaxHeads - 1) / kMaxHeads;
+    const long long max_tokens = (long long)p.max_blocks * p.block_size;
+    if (max_tokens <= 0) return -1;
+
+    // tokens per work item: 512 by default, halved while the grid cannot fill the machine,
+    // doubled while a sequence could need more than 32 splits
+    const int unit = kWarps * kTile;
+    int chunk = get_option_decode_chunk();
+    if (chunk <= 0) {
+        chunk = 512;
+        const long long base = (long long)p.num_seqs * p.kv_heads * head_blocks;
+        const long long want = 148LL * 2 * 4;
+        while (chunk > unit && base * ((max_tokens + chunk - 1) / chunk) < want) chunk >>= 1;
+        while ((max_tokens + chunk - 1) / chunk > 32) chunk <<= 1;
+    }
+    chunk = ((chunk + unit - 1) / unit) * unit;
+    const long long max_splits_ll = (max_tokens + chunk - 1) / chunk;
+    if (max_splits_ll > 65535 || p.num_seqs > 65535 || (long long)p.kv_heads * head_blocks > 65535) return -1;
+    const int max_splits = (int)max_splits_ll;
+
+    const size_t rows = (size_t)p.num_seqs * p.q_heads * max_splits;
+    const size_t acc_bytes = rows * D * sizeof(float);
+    const size_t ml_bytes = rows * sizeof(float2);
+    unsigned char* ws = static_cast<unsigned char*>(decode_workspace(stream, acc_bytes + ml_bytes));
+    if (ws == nullptr) {
+        set_last_errorf("flash_attn_with_kvcache: could not allocate %zu bytes of split-K workspace",
+                        acc_bytes + ml_bytes);
+        return FLASH_ATTN_ERR_CUDA;
+    }
+
+    DecodeArgs a{};
+    a.q = p.q; a.k = p.k; a.v = p.v;
+    a.block_tables = p.block_tables;
+    a.context_lens = p.context_lens;
+    a.ws_acc = reinterpret_cast<float*>(ws);
+    a.ws_ml = reinterpret_cast<float2*>(ws + acc_bytes);
+    a.num_seqs = p.num_seqs;
+    a.q_heads = p.q_heads;
+    a.kv_heads = p.kv_heads;
+    a.block_size = p.block_size;
+    a.max_blocks = p.max_blocks;
+    a.chunk = chunk;
+    a.max_splits = max_splits;
+    a.head_blocks = head_blocks;
+    a.scale_log2 = p.scale * 1.4426950408889634f;
+
+    cudaError_t err = cudaFuncSetAttribute(decode_splitk_kernel<T, D>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (err != cudaSuccess) {
+        set_last_errorf("decode_splitk_kernel: %s", cudaGetErrorString(err));
+        cudaGetLastError();
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    dim3 grid(max_splits, p.kv_heads * head_blocks, p.num_seqs);
+    decode_splitk_kernel<T, D><<<grid, kThreads, S::kBytes, stream>>>(a);
+    int rc = check_launch("decode_splitk_kernel");
+    if (rc != FLASH_ATTN_OK) return rc;
+    dim3 mgrid(p.q_heads, p.num_seqs);
+    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, p.context_lens,
+                                                      static_cast<T*>(p.o), p.q_heads, chunk, max_splits);
+    rc = check_launch("decode_merge_kernel");
+    if (rc == FLASH_ATTN_OK) note_path("decode_splitk", 2);
+    return rc;
+}
+
+}  // namespace
+
+int launch_decode_splitk(const AttnParams& p, cudaStream_t stream) {
+    if (p.mode != MODE_KVCACHE || p.q_seq_len != 1) return -1;
+    if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
+    if (p.head_size != 64 && p.head_size != 128) return -1;
+    if (p.q_heads > 65535) return -1;
+    // 16-byte cp.async needs 16-byte aligned rows
+    if ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) return -1;
+    if (reinterpret_cast<uintptr_t>(p.q) & 3) return -1;
+    if (p.dtype == DT_BF16) {
+        return p.head_size == 128 ? launch_typed<__nv_bfloat16, 128>(p, stream)
+                                  : launch_typed<__nv_bfloat16, 64>(p, stream);
+    }
+    return p.head_size == 128 ? launch_typed<__half, 128>(p, stream) : launch_typed<__half, 64>(p, stream);
+}
+
+}  // namespace fa

@@ -1,0 +1,60 @@
+"""Head-sharded attention across the GPUs of one box, joined by ONE all-gather of the outputs.
+
+Plays the role of luma-dist's `Comm::all_gather(&tensor, dim)` (luma-dist/src/base/comm.rs:212-214
+-> backends/nccl/backend.rs:167-180 -> backends/nccl/mod.rs:56-64) for the attention output. The
+reference has no sharded attention: its all-gather permutes `dim` to the front, materialises,
+zero-fills the receive buffer, gathers, permutes back and materialises again
+(luma-dist/src/utils.rs:12-37). Here each rank's (B, S, H_local, d) output goes through a single
+ncclAllGather into a persistent (G, B*S, H_local*d) staging buffer and one strided copy into the
+final (B, S, G*H_local, d) tensor — no memset, no input-side copy.
+
+Partitioning (rank g of G): KV heads [g*Hkv/G, (g+1)*Hkv/G) and the Hq/Hkv query heads of each.
+G must divide Hkv. Block tables and context lengths are replicated.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_heads(n_q_heads: int, n_kv_heads: int, world: int, rank: int) -> Tuple[slice, slice]:
+    """Query-head and KV-head slices owned by `rank`; whole KV groups stay together."""
+    if n_kv_heads % world != 0:
+        raise ValueError(f"world size {world} must divide kv heads {n_kv_heads}")
+    if n_q_heads % n_kv_heads != 0:
+        raise ValueError("q heads must be a multiple of kv heads")
+    kv_per = n_kv_heads // world
+    group = n_q_heads // n_kv_heads
+    kv = slice(rank * kv_per, (rank + 1) * kv_per)
+    q = slice(kv.start * group, kv.stop * group)
+    return q, kv
+
+
+class HeadAllGather:
+    """all_gather of (B, S, H_local, d) along the head axis into a reused (B, S, G*H_local, d)."""
+
+    def __init__(self, group, local_shape, dtype, device):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        b, s, h, d = local_shape
+        self.local_shape = tuple(local_shape)
+        self.staging = torch.empty((self.world, b * s, h * d), dtype=dtype, device=device)
+        self.out = torch.empty((b, s, self.world * h, d), dtype=dtype, device=device)
+        self.launches = 2  # the NCCL kernel and the interleaving copy
+
+    def __call__(self, o_local: torch.Tensor) -> torch.Tensor:
+        assert tuple(o_local.shape) == self.local_shape and o_local.is_contiguous()
+        b, s, h, d = self.local_shape
+        dist.all_gather_into_tensor(self.staging, o_local.view(b * s, h * d), group=self.group)
+        # (G, B*S, H*d) -> (B*S, G, H*d): one pass over the gathered data
+        self.out.view(b * s, self.world, h * d).copy_(self.staging.permute(1, 0, 2))
+        return self.out
+
+
+def all_gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
+    """One-shot form of HeadAllGather (allocates its buffers); also runs on the gloo backend."""
+    group = group if group is not None else dist.group.WORLD
+    g = HeadAllGather(group, o_local.shape, o_local.dtype, o_local.device)
+    return g(o_local.contiguous())

@@ -1,0 +1,85 @@
+"""ctypes declarations of libflash_attn's C ABI; mirrors luma-flash-attn/src/api/ffi.rs:6-193.
+
+The library is loaded from luma_b200/lib/libflash_attn.so (built by luma_b200/build.py). A missing
+library is an ImportError: there is no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libflash_attn.so"
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m luma_b200.build` "
+        "(needs nvcc; the attention op has no CPU or PyTorch fallback)"
+    )
+
+lib = ctypes.CDLL(str(LIB_PATH), mode=ctypes.RTLD_LOCAL)
+
+DTYPE_SUFFIX = ("f32", "f16", "bf16")
+
+_BATCH_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p,
+               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+_BATCH_LSE_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+_VARLEN_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+_KVCACHE_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+
+#: every symbol include/flash_attn.h declares
+EXPORTED_SYMBOLS = (
+    [f"flash_attn_{s}" for s in DTYPE_SUFFIX]
+    + [f"flash_attn_varlen_{s}" for s in DTYPE_SUFFIX]
+    + [f"flash_attn_with_kvcache_{s}" for s in DTYPE_SUFFIX]
+    + ["flash_attn_last_error"]
+    + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
+    + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_last_path",
+       "flash_attn_last_launches", "flash_attn_set_option"]
+)
+
+for _s in DTYPE_SUFFIX:
+    getattr(lib, f"flash_attn_{_s}").argtypes = _BATCH_ARGS
+    getattr(lib, f"flash_attn_{_s}").restype = c_int
+    getattr(lib, f"flash_attn_{_s}_lse").argtypes = _BATCH_LSE_ARGS
+    getattr(lib, f"flash_attn_{_s}_lse").restype = c_int
+    getattr(lib, f"flash_attn_varlen_{_s}").argtypes = _VARLEN_ARGS
+    getattr(lib, f"flash_attn_varlen_{_s}").restype = c_int
+    getattr(lib, f"flash_attn_with_kvcache_{_s}").argtypes = _KVCACHE_ARGS
+    getattr(lib, f"flash_attn_with_kvcache_{_s}").restype = c_int
+
+lib.flash_attn_last_error.argtypes = []
+lib.flash_attn_last_error.restype = c_char_p
+lib.flash_attn_version.argtypes = []
+lib.flash_attn_version.restype = c_char_p
+lib.flash_attn_last_path.argtypes = []
+lib.flash_attn_last_path.restype = c_char_p
+lib.flash_attn_last_launches.argtypes = []
+lib.flash_attn_last_launches.restype = c_int
+lib.flash_attn_set_option.argtypes = [c_char_p, c_int]
+lib.flash_attn_set_option.restype = c_int
+lib.flash_attn_debug_block_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+lib.flash_attn_debug_block_slots.restype = c_int
+
+
+def last_error() -> str:
+    """flash_attn_last_error() as str; NULL is treated as "" like error.rs:66-75."""
+    p = lib.flash_attn_last_error()
+    return "" if p is None else p.decode("utf-8", "replace")
+
+
+def last_path() -> str:
+    p = lib.flash_attn_last_path()
+    return "" if p is None else p.decode()
+
+
+def last_launches() -> int:
+    return int(lib.flash_attn_last_launches())
+
+
+def set_option(name: str, value: int) -> None:
+    if lib.flash_attn_set_option(name.encode(), int(value)) != 0:
+        raise KeyError(name)

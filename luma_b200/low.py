@@ -1,0 +1,134 @@
+"""Device-buffer API; mirrors luma-flash-attn/src/api/low.rs.
+
+Buffers are torch CUDA tensors used purely as typed device memory (the role cudarc's
+CudaSlice<T> plays in the reference): `numel()` is the slice length, `data_ptr()` the pointer.
+Dims are explicit i32 arguments and the layout is assumed dense, exactly as in low.rs. `stream`
+is a torch.cuda.Stream or None (the tensor's current stream).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import error as E
+from . import ffi
+
+_SUFFIX = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}
+
+
+def _suffix(t: torch.Tensor) -> str:
+    """FlashDtype dispatch (low.rs:14-134): f32 / f16 / bf16 only."""
+    try:
+        return _SUFFIX[t.dtype]
+    except KeyError:
+        raise E.Unsupported(f"dtype {t.dtype} (only f32/f16/bf16)") from None
+
+
+def _stream_ptr(stream, ref: torch.Tensor) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream(ref.device)
+    return int(stream.cuda_stream)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check_len(name: str, actual: int, need: int) -> None:
+    """low.rs:409-416"""
+    if actual >= need:
+        return
+    raise E.BufferTooSmall(f"{name}: need at least {need} elements, got {actual}")
+
+
+def _validate(q, k, v, o, batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size,
+              start_pos, attn_mask) -> None:
+    """low.rs:360-407 — same order, same error classes."""
+    if batch <= 0 or q_seq_len <= 0 or kv_seq_len <= 0 or q_num_heads <= 0 or kv_num_heads <= 0:
+        raise E.InvalidShape(
+            f"batch={batch} q_seq_len={q_seq_len} kv_seq_len={kv_seq_len} "
+            f"q_num_heads={q_num_heads} kv_num_heads={kv_num_heads} must be positive")
+    if q_num_heads % kv_num_heads != 0:
+        raise E.InvalidShape(
+            f"q_num_heads={q_num_heads} must be a multiple of kv_num_heads={kv_num_heads} (GQA)")
+    if start_pos < 0:
+        raise E.InvalidStartPos(f"start_pos={start_pos}")
+    if head_size not in (32, 64, 128):
+        raise E.InvalidHeadSize(f"head_size={head_size} (only 32/64/128)")
+    q_need = batch * q_seq_len * q_num_heads * head_size
+    kv_need = batch * kv_seq_len * kv_num_heads * head_size
+    _check_len("q", q.numel(), q_need)
+    _check_len("k", k.numel(), kv_need)
+    _check_len("v", v.numel(), kv_need)
+    _check_len("o", o.numel(), q_need)
+    if attn_mask is not None:
+        _check_len("attn_mask", attn_mask.numel(), batch * kv_seq_len)
+
+
+def flash_attn(q, k, v, o, batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size,
+               start_pos, scale, attn_mask=None, stream=None, lse=None) -> None:
+    """Batched causal attention on device buffers (low.rs:146-197).
+
+    q/o are (batch, q_seq_len, q_num_heads, head_size), k/v (batch, kv_seq_len, kv_num_heads,
+    head_size), attn_mask (batch, kv_seq_len) uint8. `lse` (optional f32 buffer of
+    batch*q_num_heads*q_seq_len) is this library's additive output.
+    """
+    _validate(q, k, v, o, batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size,
+              start_pos, attn_mask)
+    sfx = _suffix(q)
+    if lse is not None:
+        _check_len("lse", lse.numel(), batch * q_num_heads * q_seq_len)
+        code = getattr(ffi.lib, f"flash_attn_{sfx}_lse")(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), batch, q_seq_len, kv_seq_len,
+            q_num_heads, kv_num_heads, head_size, start_pos, scale, _ptr(attn_mask),
+            _stream_ptr(stream, q))
+    else:
+        code = getattr(ffi.lib, f"flash_attn_{sfx}")(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, q_seq_len, kv_seq_len, q_num_heads,
+            kv_num_heads, head_size, start_pos, scale, _ptr(attn_mask), _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
+
+
+def flash_attn_f32(*args, **kwargs) -> None:
+    """Historical alias kept by the reference (low.rs:199-218)."""
+    flash_attn(*args, **kwargs)
+
+
+def flash_attn_varlen(q, k, v, o, cu_seqlens_q, cu_seqlens_k, num_seqs, max_seqlen_q, max_seqlen_k,
+                      q_heads, kv_heads, head_size, scale, block_tables=None, block_size=1,
+                      stream=None) -> None:
+    """Packed variable-length attention (low.rs:231-295). With `block_tables` the K/V are a paged
+    cache and max_blocks is inferred as block_tables.numel() // num_seqs (low.rs:266-269)."""
+    sfx = _suffix(q)
+    k_paged = 1 if block_tables is not None else 0
+    max_blocks = (block_tables.numel() // num_seqs) if (block_tables is not None and num_seqs > 0) else 0
+    code = getattr(ffi.lib, f"flash_attn_varlen_{sfx}")(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
+        _ptr(block_tables), num_seqs, max_seqlen_q, max_seqlen_k, q_heads, kv_heads, head_size,
+        block_size, max_blocks, k_paged, scale, _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
+
+
+def flash_attn_with_kvcache(q, k_cache, v_cache, o, block_tables, context_lens, num_seqs, q_seq_len,
+                            q_heads, kv_heads, head_size, block_size, max_blocks, scale,
+                            stream=None) -> None:
+    """Attention over a paged KV cache (low.rs:305-357): q_seq_len == 1 decodes, > 1 prefills."""
+    if q_seq_len <= 0:
+        raise E.InvalidShape(f"q_seq_len={q_seq_len} must be > 0")
+    q_need = num_seqs * q_seq_len * q_heads * head_size
+    _check_len("q", q.numel(), q_need)
+    _check_len("o", o.numel(), q_need)
+    sfx = _suffix(q)
+    code = getattr(ffi.lib, f"flash_attn_with_kvcache_{sfx}")(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(o), _ptr(block_tables), _ptr(context_lens),
+        num_seqs, q_seq_len, q_heads, kv_heads, head_size, block_size, max_blocks, scale,
+        _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
+
+
+def debug_block_slots(block_tables, context_lens, offsets, num_seqs, block_size, max_blocks,
+                      out_slots, stream=None) -> None:
+    """Device-side block_slot() of every cached token, for the bit-exact page-index check."""
+    code = ffi.lib.flash_attn_debug_block_slots(
+        _ptr(block_tables), _ptr(context_lens), _ptr(offsets), num_seqs, block_size, max_blocks,
+        _ptr(out_slots), _stream_ptr(stream, block_tables))
+    E.from_status(code, ffi.last_error())
