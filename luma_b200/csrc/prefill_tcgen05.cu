@@ -1,5 +1,640 @@
-// placeholder until the tcgen05 kernel lands
+// Causal, GQA-capable flash-attention prefill forward for sm_100a: TMA-fed Q/K/V tiles,
+// tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
+// warp-specialised roles. Handles f16/bf16 storage with head_size 128, no padding mask, for the
+// batched entry point. Replaces flash_attn_kernel (luma-flash-attn/kernels/flash_attn_func.cu:29-226),
+// a one-thread-per-query-row scalar kernel.
+//
+// One CTA (320 threads, 1 per SM) owns up to two query tiles of 128 rows that share a batch
+// element and a KV head — two query heads of one GQA group at the same row block, or two
+// consecutive row blocks of one head when the group is 1 — and streams that KV head's K/V tiles
+// (128 keys) past both:
+//   warps 0-3 / 4-7 : softmax warpgroup of query tile 0 / 1 — one thread per query row: read S
+//                     from tensor memory (tcgen05.ld), running max / sum in registers (exp2 with
+//                     the scale folded in), write P as packed 16-bit back over S (tcgen05.st),
+//                     rescale O in tensor memory only when the row max moved by more than 2^8,
+//                     final normalisation and store of O (and LSE)
+//   warp 8          : TMA producer — Q once, then K and V tiles through two 2-stage rings
+//   warp 9          : MMA issuer — S_t = Q_t K^T (SS form), O_t += P_t V (P from tensor memory),
+//                     completion signalled with tcgen05.commit on mbarriers
+// While one warpgroup runs its softmax the tensor core works on the other tile.
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t aliases S_t.
+// Shared memory: Q 2 x 32 KiB, K ring 2 x 32 KiB, V ring 2 x 32 KiB, all 128-byte swizzled
+// exactly as TMA writes them, so the MMA descriptors address them in place.
+//
+// Every wait on an mbarrier is bounded (about 2 s of wall clock); on expiry the CTA records a
+// status word in global memory, stops waiting everywhere, drains its own TMA copies, frees its
+// tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+
 namespace fa {
-int launch_prefill_tcgen05(const AttnParams&, cudaStream_t) { return -1; }
+
+namespace {
+
+constexpr int kBlockM = 128;   // query rows per tile
+constexpr int kBlockN = 128;   // keys per K/V tile
+constexpr int kD = 128;        // head size
+constexpr int kStages = 2;     // K ring and V ring depth
+constexpr int kThreads = 320;
+constexpr int kLoadWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kTileBytes = kBlockN * kD * 2;        // 32 KiB: two 64-column halves of 128 rows x 128 B
+constexpr int kHalfBytes = kTileBytes / 2;
+constexpr float kRescaleThreshold = 8.0f;            // log2 units
+
+struct SharedStorage {
+    alignas(1024) unsigned char q[2][kTileBytes];
+    alignas(1024) unsigned char k[kStages][kTileBytes];
+    alignas(1024) unsigned char v[kStages][kTileBytes];
+    alignas(8) unsigned long long q_full[2];
+    unsigned long long k_full[kStages], k_empty[kStages];
+    unsigned long long v_full[kStages], v_empty[kStages];
+    unsigned long long s_full[2];   // MMA -> softmax: S_t ready (and every earlier MMA finished)
+    unsigned long long p_full[2];   // softmax -> MMA: P_t written, O_t rescaled
+    unsigned int tmem_base;
+    volatile int abort_flag;
+};
+
+struct PrefillArgs {
+    void* o;
+    float* lse;
+    int* status;    // device word, set to non-zero when a bounded wait expired
+    int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
+    float scale_log2;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
+
+// Bounded wait. Returns false when the wait was abandoned (time limit, or another thread of the
+// CTA already gave up); the caller then falls through to the end of the kernel.
+__device__ __forceinline__ bool mbar_wait(SharedStorage& sm, unsigned long long* bar, unsigned parity, int* status,
+                                          int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (unsigned spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (sm.abort_flag) return false;
+            if (global_timer_ns() - t0 > 2000000000ULL) {
+                sm.abort_flag = 1;
+                atomicCAS(status, 0, where);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, unsigned long long* bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp <-> TMEM lane (base + i)
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&r)[32]) {
+    unsigned* u = reinterpret_cast<unsigned*>(r);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+          "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+          "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(unsigned taddr, const unsigned (&u)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(
+            taddr),
+        "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]),
+        "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]), "r"(u[18]),
+        "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]),
+        "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T> __device__ __forceinline__ unsigned pack16(float lo, float hi);
+template <> __device__ __forceinline__ unsigned pack16<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&t);
+}
+template <> __device__ __forceinline__ unsigned pack16<__half>(float lo, float hi) {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&t);
+}
+
+// Shared-memory matrix descriptor (tcgen05): 128-byte swizzle, descriptor version 1.
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1      bits [61,64) layout = 2 (SWIZZLE_128B)
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ULL << 46;
+    d |= 2ULL << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: f32 accumulate, A/B both f16 or both bf16, M = 128, N = 128.
+//   bits [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
+//   bit 15 A major, bit 16 B major (0 = K-major, 1 = MN-major)  [17,23) N >> 3  [24,29) M >> 4
+template <typename T>
+__device__ __forceinline__ unsigned make_idesc(bool b_mn_major) {
+    const unsigned fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    unsigned d = 0;
+    d |= 1u << 4;
+    d |= fmt << 7;
+    d |= fmt << 10;
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= (unsigned)(kBlockN >> 3) << 17;
+    d |= (unsigned)(kBlockM >> 4) << 24;
+    return d;
+}
+
+struct TileInfo {
+    int valid;    // this query tile exists
+    int head;     // query head
+    int row0;     // first query row
+    int n_kv;     // K/V tiles it needs
+};
+
+__device__ __forceinline__ TileInfo tile_info(const PrefillArgs& a, int pair, int t, int kvh, int group, int num_mb) {
+    TileInfo ti;
+    const int idx = pair * 2 + t;
+    ti.valid = idx < group * num_mb;
+    const int mb = ti.valid ? idx / group : 0;
+    ti.head = kvh * group + (ti.valid ? idx - mb * group : 0);
+    ti.row0 = mb * kBlockM;
+    const int last_row = min(ti.row0 + kBlockM, a.q_seq_len) - 1;
+    const long long last_key = min((long long)a.kv_seq_len - 1, (long long)a.start_pos + last_row);
+    ti.n_kv = ti.valid ? (int)(last_key / kBlockN) + 1 : 0;
+    return ti;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    SharedStorage& sm = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int group = a.q_heads / a.kv_heads;
+    const int num_mb = (a.q_seq_len + kBlockM - 1) / kBlockM;
+    const int kvh = blockIdx.x % a.kv_heads;
+    const int b = blockIdx.x / a.kv_heads;
+    const int pair = gridDim.y - 1 - blockIdx.y;   // heaviest (latest rows) first
+
+    const TileInfo t0 = tile_info(a, pair, 0, kvh, group, num_mb);
+    const TileInfo t1 = tile_info(a, pair, 1, kvh, group, num_mb);
+    const int n_max = max(t0.n_kv, t1.n_kv);
+
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sm.q_full[i], 1);
+            mbar_init(&sm.s_full[i], 1);
+            mbar_init(&sm.p_full[i], 128);
+        }
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sm.k_full[i], 1);
+            mbar_init(&sm.k_empty[i], 1);
+            mbar_init(&sm.v_full[i], 1);
+            mbar_init(&sm.v_empty[i], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(smem_u32(&sm.tmem_base)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = sm.tmem_base;
+
+    if (warp == kLoadWarp) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const TileInfo ts[2] = {t0, t1};
+            for (int t = 0; t < 2; ++t) {
+                if (!ts[t].valid) continue;
+                mbar_expect_tx(&sm.q_full[t], kTileBytes);
+                tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ts[t].head, ts[t].row0, b);
+                tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ts[t].head, ts[t].row0, b);
+            }
+            bool alive = true;
+            for (int j = 0; j < n_max && alive; ++j) {
+                const int s = j % kStages;
+                const unsigned ph = (unsigned)(j / kStages) & 1u;
+                alive = mbar_wait(sm, &sm.k_empty[s], ph ^ 1u, a.status, 1);
+                if (!alive) break;
+                mbar_expect_tx(&sm.k_full[s], kTileBytes);
+                tma_load_4d(sm.k[s], &k_map, &sm.k_full[s], 0, kvh, j * kBlockN, b);
+                tma_load_4d(sm.k[s] + kHalfBytes, &k_map, &sm.k_full[s], 64, kvh, j * kBlockN, b);
+                alive = mbar_wait(sm, &sm.v_empty[s], ph ^ 1u, a.status, 2);
+                if (!alive) break;
+                mbar_expect_tx(&sm.v_full[s], kTileBytes);
+                tma_load_4d(sm.v[s], &v_map, &sm.v_full[s], 0, kvh, j * kBlockN, b);
+                tma_load_4d(sm.v[s] + kHalfBytes, &v_map, &sm.v_full[s], 64, kvh, j * kBlockN, b);
+            }
+            // Make sure none of this CTA's bulk copies is still in flight when it exits: wait
+            // (bounded) for the last fill of every stage and of the Q tiles.
+            for (int t = 0; t < 2; ++t)
+                if (ts[t].valid) mbar_wait(sm, &sm.q_full[t], 0, a.status, 3);
+            for (int s = 0; s < kStages; ++s) {
+                // last j with j % kStages == s that was actually issued
+                int last = -1;
+                for (int j = s; j < n_max; j += kStages) last = j;
+                if (last >= 0) {
+                    const unsigned ph = (unsigned)(last / kStages) & 1u;
+                    // ignore the abort flag here: these waits only depend on the copy engine
+                    const unsigned long long t_begin = global_timer_ns();
+                    while (!mbar_try_wait(&sm.k_full[s], ph) && global_timer_ns() - t_begin < 100000000ULL) {}
+                    while (!mbar_try_wait(&sm.v_full[s], ph) && global_timer_ns() - t_begin < 100000000ULL) {}
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const unsigned idesc_qk = make_idesc<T>(false);
+            const unsigned idesc_pv = make_idesc<T>(true);
+            const TileInfo ts[2] = {t0, t1};
+            bool alive = true;
+            auto issue_s = [&](int t, int stage) {
+                // S_t = Q_t K^T : 8 K-steps of 16 over d; both operands K-major, 128 B swizzle
+                const unsigned qa = smem_u32(sm.q[t]);
+                const unsigned kb = smem_u32(sm.k[stage]);
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const unsigned off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+                    tc_mma_ss(tmem + t * 128, make_desc(qa + off, 16, 1024), make_desc(kb + off, 16, 1024), idesc_qk,
+                              kk > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int stage, bool accumulate) {
+                // O_t += P_t V : 8 K-steps of 16 keys; A = P from tensor memory (packed 16-bit, 8 columns
+                // per step), B = V MN-major: 64-column halves 16 KiB apart, 8-key groups 1 KiB apart
+                const unsigned vb = smem_u32(sm.v[stage]);
+#pragma unroll
+                for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                    tc_mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, make_desc(vb + kk * 2048, kHalfBytes, 1024),
+                              idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                }
+            };
+            for (int t = 0; t < 2 && alive; ++t)
+                if (ts[t].valid) alive = mbar_wait(sm, &sm.q_full[t], 0, a.status, 10);
+            if (alive && n_max > 0) alive = mbar_wait(sm, &sm.k_full[0], 0, a.status, 11);
+            if (alive && n_max > 0) {
+                tc_fence_after();
+                for (int t = 0; t < 2; ++t) {
+                    if (ts[t].n_kv > 0) {
+                        issue_s(t, 0);
+                        tc_commit(&sm.s_full[t]);
+                    }
+                }
+                tc_commit(&sm.k_empty[0]);
+            }
+            for (int j = 0; j < n_max && alive; ++j) {
+                const int s = j % kStages;
+                const unsigned ph = (unsigned)(j / kStages) & 1u;
+                const int s1 = (j + 1) % kStages;
+                const unsigned ph1 = (unsigned)((j + 1) / kStages) & 1u;
+                if (j + 1 < n_max) {
+                    alive = mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12);
+                    if (!alive) break;
+                }
+                alive = mbar_wait(sm, &sm.v_full[s], ph, a.status, 13);
+                if (!alive) break;
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= ts[t].n_kv) continue;
+                    alive = mbar_wait(sm, &sm.p_full[t], (unsigned)j & 1u, a.status, 14 + t);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_pv(t, s, j > 0);
+                    if (j + 1 < ts[t].n_kv) issue_s(t, s1);
+                    tc_commit(&sm.s_full[t]);   // S_t(j+1) ready, or after the last PV: O_t final
+                }
+                if (!alive) break;
+                tc_commit(&sm.v_empty[s]);
+                if (j + 1 < n_max) tc_commit(&sm.k_empty[s1]);
+            }
+        }
+    } else {
+        // ------------------------------ softmax warpgroups ------------------------------
+        const int t = warp >> 2;
+        const TileInfo ti = t == 0 ? t0 : t1;
+        const int r = (warp & 3) * 32 + lane;                  // row within the tile == TMEM lane
+        const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
+        const unsigned s_addr = tmem + lane_base + t * 128;
+        const unsigned o_addr = tmem + lane_base + 256 + t * 128;
+        const int row = ti.row0 + r;
+        const long long pos = (long long)a.start_pos + row;     // global position of this query row
+        float m = -INFINITY;   // reference max, log2 domain (may lag the true max by <= 2^8)
+        float l = 0.0f;
+        bool alive = true;
+
+        for (int j = 0; j < ti.n_kv && alive; ++j) {
+            alive = mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a.status, 20 + t);
+            if (!alive) break;
+            tc_fence_after();
+            float sv[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
+            tc_wait_ld();
+
+            const int key0 = j * kBlockN;
+            // mask only where the causal diagonal or the end of K/V cuts through this tile
+            const long long limit_ll = min(pos, (long long)a.kv_seq_len - 1) - key0;
+            const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)a.start_pos + ti.row0, (long long)a.kv_seq_len - 1);
+            if (need_mask) {
+                const int limit = (int)max(-1LL, min(limit_ll, (long long)kBlockN));
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i > limit) sv[c][i] = -INFINITY;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[c][i]);
+            mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
+
+            float alpha = 1.0f;
+            bool changed = false;
+            if (mx > m + kRescaleThreshold) {   // also true for the first finite max (m == -inf)
+                alpha = ex2(m - mx);            // 0 when m == -inf
+                m = mx;
+                changed = true;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, changed)) {
+                // rescale this warp's 32 rows of O in tensor memory (rows that did not move use 1.0)
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    float ov[32];
+                    tc_ld32(o_addr + c * 32, ov);
+                    tc_wait_ld();
+                    unsigned ou[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ou[i] = __float_as_uint(ov[i] * alpha);
+                    tc_st32(o_addr + c * 32, ou);
+                }
+            }
+            const float m_use = (m == -INFINITY) ? 0.0f : m;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                unsigned pu[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int cc = c * 2 + (i >> 4);
+                    const int ii = (i & 15) * 2;
+                    const float p0 = ex2(fmaf(sv[cc][ii], a.scale_log2, -m_use));
+                    const float p1 = ex2(fmaf(sv[cc][ii + 1], a.scale_log2, -m_use));
+                    sum += p0 + p1;
+                    pu[i] = pack16<T>(p0, p1);
+                }
+                tc_st32(s_addr + c * 32, pu);
+            }
+            l = l * alpha + sum;
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.p_full[t]);
+        }
+
+        // epilogue: O_t is final once the commit after the last P.V has arrived
+        if (alive && ti.n_kv > 0) alive = mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a.status, 30 + t);
+        if (alive && ti.valid) {
+            tc_fence_after();
+            const bool row_ok = row < a.q_seq_len;
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            T* orow = static_cast<T*>(a.o) + (((long long)b * a.q_seq_len + row) * a.q_heads + ti.head) * kD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float ov[32];
+                tc_ld32(o_addr + c * 32, ov);
+                tc_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack16<T>(ov[i] * inv, ov[i + 1] * inv);
+                        w.y = pack16<T>(ov[i + 2] * inv, ov[i + 3] * inv);
+                        w.z = pack16<T>(ov[i + 4] * inv, ov[i + 5] * inv);
+                        w.w = pack16<T>(ov[i + 6] * inv, ov[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                    }
+                }
+            }
+            if (row_ok && a.lse != nullptr) {
+                a.lse[((long long)b * a.q_heads + ti.head) * a.q_seq_len + row] =
+                    l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []() {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeFn>(p);
+        } else {
+            cudaGetLastError();
+        }
+    });
+    return fn;
+}
+
+// (batch, seq, heads, 128) 16-bit tensor viewed as 4-D {d, head, seq, batch}; box = 64 x 1 x 128 x 1
+bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2, (cuuint64_t)seq * heads * kD * 2};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)kBlockM, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult rc = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+std::mutex g_status_mutex;
+int* g_status_word[64] = {nullptr};
+
+int* status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (g_status_word[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cudaMemset(p, 0, sizeof(int));
+        g_status_word[dev] = p;
+    }
+    return g_status_word[dev];
+}
+
+template <typename T>
+int launch_typed(const AttnParams& p, cudaStream_t stream) {
+    CUtensorMap qm, km, vm;
+    if (!encode_map(&qm, p.q, p.dtype, p.num_seqs, p.q_seq_len, p.q_heads) ||
+        !encode_map(&km, p.k, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads) ||
+        !encode_map(&vm, p.v, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads)) {
+        return -1;  // let the SIMT kernel take it
+    }
+    int* status = status_word();
+    if (status == nullptr) return -1;
+
+    PrefillArgs a{};
+    a.o = p.o;
+    a.lse = p.lse;
+    a.status = status;
+    a.batch = p.num_seqs;
+    a.q_seq_len = p.q_seq_len;
+    a.kv_seq_len = p.kv_seq_len;
+    a.q_heads = p.q_heads;
+    a.kv_heads = p.kv_heads;
+    a.start_pos = p.start_pos;
+    a.scale_log2 = p.scale * 1.4426950408889634f;
+
+    const int group = p.q_heads / p.kv_heads;
+    const int num_mb = (p.q_seq_len + kBlockM - 1) / kBlockM;
+    const int pairs = (group * num_mb + 1) / 2;
+    const size_t smem = sizeof(SharedStorage) + 1024;
+    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+        set_last_errorf("prefill_tcgen05_kernel: %s", cudaGetErrorString(err));
+        cudaGetLastError();
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    dim3 grid(p.kv_heads * p.num_seqs, pairs);
+    prefill_tcgen05_kernel<T><<<grid, kThreads, smem, stream>>>(qm, km, vm, a);
+    const int rc = check_launch("prefill_tcgen05_kernel");
+    if (rc == FLASH_ATTN_OK) note_path("prefill_tcgen05", 1);
+    return rc;
+}
+
+}  // namespace
+
+int prefill_device_status() {
+    int* status = status_word();
+    if (status == nullptr) return -1;
+    int h = 0;
+    if (cudaMemcpy(&h, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    if (h != 0) cudaMemset(status, 0, sizeof(int));
+    return h;
+}
+
+int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
+    if (p.mode != MODE_BATCH || p.mask != nullptr) return -1;
+    if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
+    if (p.head_size != kD) return -1;
+    if (!(p.scale > 0.0f)) return -1;
+    if (p.q_seq_len < 16) return -1;   // a handful of rows is not worth a 128-row tile
+    const uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
+                            reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.o);
+    if (align & 15) return -1;
+    const long long pairs = ((long long)(p.q_heads / p.kv_heads) * ((p.q_seq_len + kBlockM - 1) / kBlockM) + 1) / 2;
+    if (pairs > 65535) return -1;
+    return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16>(p, stream) : launch_typed<__half>(p, stream);
+}
+
+}  // namespace fa
