@@ -178,7 +178,14 @@ int flash_attn_debug_block_slots(const int* block_tables, const int* context_len
  *       "force_generic"       1 = route everything through the SIMT tile kernel
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  */
+/*
+ *   flash_attn_device_status  : synchronises the current device, then reads and clears its status
+ *                               word. 0 = healthy. Non-zero = a bounded wait inside the tcgen05
+ *                               prefill kernel expired (the value names the wait) and the outputs
+ *                               of that launch are undefined; -1 = no device / not readable.
+ */
 const char* flash_attn_version(void);
+int flash_attn_device_status(void);
 const char* flash_attn_last_path(void);
 int flash_attn_last_launches(void);
 int flash_attn_set_option(const char* name, int value);

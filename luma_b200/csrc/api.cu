@@ -296,6 +296,11 @@ const char* flash_attn_version(void) { return "luma-b200-flash-attn 0.1.0 (sm_10
 const char* flash_attn_last_path(void) { return fa::g_last_path; }
 int flash_attn_last_launches(void) { return fa::g_last_launches; }
 
+int flash_attn_device_status(void) {
+    if (!fa::have_device()) return -1;
+    return fa::prefill_device_status();
+}
+
 int flash_attn_set_option(const char* name, int value) {
     if (name == nullptr) return 1;
     if (std::strcmp(name, "force_generic") == 0) {

@@ -125,6 +125,10 @@ int launch_debug_block_slots(const int* block_tables, const int* context_lens, c
                              int num_seqs, int block_size, int max_blocks, int* out_slots,
                              cudaStream_t stream);
 
+// Reads and clears the per-device status word of the tcgen05 kernel (0 = every bounded wait was
+// satisfied; otherwise the code of the wait that expired). Synchronises the device.
+int prefill_device_status();
+
 // Split-K scratch of the decode path: one buffer per (device, stream), grown on demand.
 void* decode_workspace(cudaStream_t stream, size_t bytes);
 

@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -407,7 +408,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         bool alive = true;
 
         for (int j = 0; j < ti.n_kv && alive; ++j) {
-            alive = mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a.status, 20 + t);
+            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a.status, 20 + t));
             if (!alive) break;
             tc_fence_after();
             float sv[4][32];
@@ -477,7 +478,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
 
         // epilogue: O_t is final once the commit after the last P.V has arrived
-        if (alive && ti.n_kv > 0) alive = mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a.status, 30 + t);
+        if (alive && ti.n_kv > 0)
+            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a.status, 30 + t));
         if (alive && ti.valid) {
             tc_fence_after();
             const bool row_ok = row < a.q_seq_len;

@@ -37,7 +37,7 @@ EXPORTED_SYMBOLS = (
     + [f"flash_attn_with_kvcache_{s}" for s in DTYPE_SUFFIX]
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
-    + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_last_path",
+    + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
 
@@ -55,6 +55,8 @@ lib.flash_attn_last_error.argtypes = []
 lib.flash_attn_last_error.restype = c_char_p
 lib.flash_attn_version.argtypes = []
 lib.flash_attn_version.restype = c_char_p
+lib.flash_attn_device_status.argtypes = []
+lib.flash_attn_device_status.restype = c_int
 lib.flash_attn_last_path.argtypes = []
 lib.flash_attn_last_path.restype = c_char_p
 lib.flash_attn_last_launches.argtypes = []
@@ -74,6 +76,11 @@ def last_error() -> str:
 def last_path() -> str:
     p = lib.flash_attn_last_path()
     return "" if p is None else p.decode()
+
+
+def device_status() -> int:
+    """Synchronises, then reads and clears the device status word (0 = healthy)."""
+    return int(lib.flash_attn_device_status())
 
 
 def last_launches() -> int:
