@@ -169,6 +169,37 @@ int flash_attn_debug_block_slots(const int* block_tables, const int* context_len
                                  void* stream);
 
 /*
+ * Paged single-token decode (bf16, head_size 64 or 128) that never allocates. It has no
+ * counterpart in the reference.
+ *
+ * Same arguments and result as flash_attn_with_kvcache_bf16 with q_seq_len == 1, but the split-K
+ * partials go to a fixed 16 MiB array inside the library image instead of a cudaMalloc'ed
+ * workspace, and the call makes no cudaMalloc / cudaFree / allocating library call at all. It is
+ * meant for callers that cannot allocate at this point: an engine that reserved all device
+ * memory for its own pool at start-up (a later cudaMalloc inside a library would fail), or a
+ * latency-critical step that must not take the driver's allocation lock and the device-wide
+ * synchronisation that cudaMalloc and cudaFree imply.
+ *   - Cost: every GPU whose context loads this library holds those 16 MiB until the process
+ *     exits, whether or not this function is called.
+ *   - Limit: the partials of one split, num_seqs * q_heads * (head_size*4 + 8) bytes, must fit in
+ *     16 MiB (32 263 rows at head_size 128); larger problems return
+ *     FLASH_ATTN_ERR_INVALID_SHAPE with a message naming the limit. Within the limit the context
+ *     is cut into as many splits as fit.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array. Nothing in it has to start at zero (every slot
+ *     that is read was written earlier in the same call), but two calls that overlap on the GPU —
+ *     different streams, or different threads — race on it; serialise them.
+ * Check order: NULL -> NULL_PTR; non-positive sizes, Hq % Hkv, head_size not in {64,128},
+ * misaligned caches, scratch too small -> INVALID_SHAPE.
+ */
+int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k_cache,
+                                   const flash_attn_bf16_t* v_cache, flash_attn_bf16_t* o,
+                                   const int* block_tables, const int* context_lens,
+                                   int num_seqs, int q_heads, int kv_heads, int head_size,
+                                   int block_size, int max_blocks, float scale, void* stream);
+
+/*
  * Tuning and introspection. No counterpart in the reference.
  *   flash_attn_version        : library version string.
  *   flash_attn_last_path      : name of the kernel family the last successful call on this

@@ -16,6 +16,8 @@
 //   * split-K over the context: every chunk writes an unnormalised f32 partial (acc, m, l) to a
 //     workspace and a second kernel merges the chunks of a sequence with log-sum-exp weights.
 // Token -> slot arithmetic is block_slot() from common.cuh (reference: kernels/common.cuh:89-108).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fa {
@@ -467,4 +469,179 @@ int launch_decode_splitk(const AttnParams& p, cudaStream_t stream) {
     return p.head_size == 128 ? launch_typed<__half, 128>(p, stream) : launch_typed<__half, 64>(p, stream);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode without any allocation: the split-K partials live in a fixed array that is part of the
+// library image instead of a cudaMalloc'ed workspace.
+//
+// Who needs this: a serving engine that hands all of HBM to its own pool at start-up leaves
+// nothing for a library-side cudaMalloc to find, so the ordinary decode entry point can fail (or
+// fragment the pool) the first time it has to size its workspace; and a caller in the middle of
+// a latency-critical step cannot afford cudaMalloc / cudaFree, which take the driver's allocation
+// lock and synchronise the whole device. For them the scratch is paid for once, when the library
+// is loaded: every GPU whose context loads libflash_attn holds kStaticScratchBytes of it until
+// the process exits, whether or not this entry point is ever called.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the
+// device address is fetched once per device with cudaGetSymbolAddress (with that device current)
+// and passed to the same two kernels the ordinary path launches.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;   // 16 MiB per GPU
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+unsigned char* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device; resolved on first use per device.
+unsigned char* static_scratch_ptr() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        set_last_error("flash_attn_decode_bf16_noalloc: cannot identify the current device");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (err != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            set_last_errorf("flash_attn_decode_bf16_noalloc: cudaGetSymbolAddress failed: %s",
+                            cudaGetErrorString(err));
+            return nullptr;
+        }
+        g_static_ptr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    return g_static_ptr[dev];
+}
+
+template <int D>
+int launch_static(const void* q, const void* k, const void* v, void* o, const int* block_tables,
+                  const int* context_lens, int num_seqs, int q_heads, int kv_heads, int block_size,
+                  int max_blocks, float scale, cudaStream_t stream) {
+    using T = __nv_bfloat16;
+    using S = Smem<D>;
+    const int group = q_heads / kv_heads;
+    const int head_blocks = (group + kMaxHeads - 1) / kMaxHeads;
+    const long long max_tokens = (long long)max_blocks * block_size;
+    const int unit = kWarps * kTile;
+
+    // one split must always fit; beyond that the chunk grows until the partials fit the array
+    const size_t row_bytes = (size_t)D * sizeof(float) + sizeof(float2);
+    const size_t rows1 = (size_t)num_seqs * q_heads;
+    if (rows1 * row_bytes > kStaticScratchBytes) {
+        set_last_errorf("flash_attn_decode_bf16_noalloc: num_seqs*q_heads = %zu exceeds the static scratch "
+                        "(%zu bytes hold at most %zu rows of head_size %d); use flash_attn_with_kvcache_bf16",
+                        rows1, kStaticScratchBytes, kStaticScratchBytes / row_bytes, D);
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    long long chunk = 512;
+    {
+        const long long base = (long long)num_seqs * kv_heads * head_blocks;
+        const long long want = 148LL * 2 * 4;
+        while (chunk > unit && base * ((max_tokens + chunk - 1) / chunk) < want) chunk >>= 1;
+        while (rows1 * (size_t)((max_tokens + chunk - 1) / chunk) * row_bytes > kStaticScratchBytes) chunk <<= 1;
+    }
+    chunk = ((chunk + unit - 1) / unit) * unit;
+    const long long max_splits_ll = (max_tokens + chunk - 1) / chunk;
+    if (chunk > 0x40000000LL || max_splits_ll > 65535 || num_seqs > 65535 || (long long)kv_heads * head_blocks > 65535 ||
+        q_heads > 65535) {
+        set_last_error("flash_attn_decode_bf16_noalloc: grid dimensions out of range");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    const int max_splits = (int)max_splits_ll;
+    const size_t rows = rows1 * max_splits;
+    const size_t acc_bytes = rows * D * sizeof(float);   // a multiple of 256 bytes, so the float2 part stays aligned
+
+    unsigned char* ws = static_scratch_ptr();
+    if (ws == nullptr) return FLASH_ATTN_ERR_CUDA;
+
+    DecodeArgs a{};
+    a.q = q; a.k = k; a.v = v;
+    a.block_tables = block_tables;
+    a.context_lens = context_lens;
+    a.ws_acc = reinterpret_cast<float*>(ws);
+    a.ws_ml = reinterpret_cast<float2*>(ws + acc_bytes);
+    a.num_seqs = num_seqs;
+    a.q_heads = q_heads;
+    a.kv_heads = kv_heads;
+    a.block_size = block_size;
+    a.max_blocks = max_blocks;
+    a.chunk = (int)chunk;
+    a.max_splits = max_splits;
+    a.head_blocks = head_blocks;
+    a.scale_log2 = scale * 1.4426950408889634f;
+
+    cudaError_t err = cudaFuncSetAttribute(decode_splitk_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           S::kBytes);
+    if (err != cudaSuccess) {
+        set_last_errorf("decode_splitk_kernel: %s", cudaGetErrorString(err));
+        cudaGetLastError();
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    dim3 grid(max_splits, kv_heads * head_blocks, num_seqs);
+    decode_splitk_kernel<T, D><<<grid, kThreads, S::kBytes, stream>>>(a);
+    int rc = check_launch("decode_splitk_kernel");
+    if (rc != FLASH_ATTN_OK) return rc;
+    dim3 mgrid(q_heads, num_seqs);
+    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, context_lens, static_cast<T*>(o), q_heads,
+                                                      (int)chunk, max_splits);
+    rc = check_launch("decode_merge_kernel");
+    if (rc == FLASH_ATTN_OK) note_path("decode_splitk_static", 2);
+    return rc;
+}
+
+}  // namespace
 }  // namespace fa
+
+extern "C" int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k_cache,
+                                              const flash_attn_bf16_t* v_cache, flash_attn_bf16_t* o,
+                                              const int* block_tables, const int* context_lens, int num_seqs,
+                                              int q_heads, int kv_heads, int head_size, int block_size,
+                                              int max_blocks, float scale, void* stream) {
+    using namespace fa;
+    set_last_error("");
+    cudaGetLastError();
+    if (!q || !k_cache || !v_cache || !o || !block_tables || !context_lens) {
+        set_last_error("flash_attn_decode_bf16_noalloc: null pointer argument");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (num_seqs <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || block_size <= 0 || max_blocks <= 0) {
+        set_last_error("flash_attn_decode_bf16_noalloc: num_seqs/heads/block_size/max_blocks must be > 0 and "
+                       "q_heads a multiple of kv_heads");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (head_size != 64 && head_size != 128) {
+        set_last_error("flash_attn_decode_bf16_noalloc: head_size must be 64 or 128");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) ||
+        (reinterpret_cast<uintptr_t>(q) & 3)) {
+        set_last_error("flash_attn_decode_bf16_noalloc: k_cache/v_cache must be 16-byte aligned, q 4-byte aligned");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    // launch on the device that owns q, and resolve the scratch address on that same device
+    int prev = -1;
+    bool switched = false;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, q) == cudaSuccess && attr.type == cudaMemoryTypeDevice &&
+        cudaGetDevice(&prev) == cudaSuccess && attr.device != prev) {
+        if (cudaSetDevice(attr.device) != cudaSuccess) {
+            cudaGetLastError();
+            set_last_error("flash_attn_decode_bf16_noalloc: could not select the device that owns q");
+            return FLASH_ATTN_ERR_CUDA;
+        }
+        switched = true;
+    }
+    cudaGetLastError();
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int rc = head_size == 128
+                       ? launch_static<128>(q, k_cache, v_cache, o, block_tables, context_lens, num_seqs, q_heads,
+                                            kv_heads, block_size, max_blocks, scale, st)
+                       : launch_static<64>(q, k_cache, v_cache, o, block_tables, context_lens, num_seqs, q_heads,
+                                           kv_heads, block_size, max_blocks, scale, st);
+    if (switched) cudaSetDevice(prev);
+    return rc;
+}

@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     + [f"flash_attn_with_kvcache_{s}" for s in DTYPE_SUFFIX]
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
+    + ["flash_attn_decode_bf16_noalloc"]
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
@@ -51,6 +52,9 @@ for _s in DTYPE_SUFFIX:
     getattr(lib, f"flash_attn_with_kvcache_{_s}").argtypes = _KVCACHE_ARGS
     getattr(lib, f"flash_attn_with_kvcache_{_s}").restype = c_int
 
+lib.flash_attn_decode_bf16_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+lib.flash_attn_decode_bf16_noalloc.restype = c_int
 lib.flash_attn_last_error.argtypes = []
 lib.flash_attn_last_error.restype = c_char_p
 lib.flash_attn_version.argtypes = []
