@@ -309,10 +309,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default=None, help="run just one workload: prefill_c2, prefill_c3, decode_c4, prefill_c5, decode_c5")
+    ap.add_argument("--profile", default=None,
+                    help="run ONE workload and nothing else (for ncu): prefill_c2, prefill_c3, prefill_c3_small, "
+                         "decode_c4, decode_c4_small, decode_c5")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--small", action="store_true", help="shrink every workload (for profiler captures)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small else args.warmup
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small and not args.profile else args.warmup
 
     if args.impl == "reference":
         reference_arm(args)
@@ -337,6 +340,31 @@ def main():
     def barrier():
         if dist is not None:
             dist.barrier()
+
+    if args.profile:
+        # one workload, nothing else: the command line the ncu summaries under profiles/ were made with
+        name = args.profile
+        if name == "prefill_c2":
+            res, _ = run_prefill(torch, low, ffi, dev, name, 4, 32, 32, 2048, 128, args.steps, args.warmup, peaks, seed=2)
+        elif name == "prefill_c3":
+            res, _ = run_prefill(torch, low, ffi, dev, name, 2, 32, 8, 8192, 128, args.steps, args.warmup, peaks, seed=3,
+                                 scale_in=0.5, want_lse=False)
+        elif name == "prefill_c3_small":   # one batch element, 8 of 32 heads: same kernel, short capture
+            res, _ = run_prefill(torch, low, ffi, dev, name, 1, 8, 2, 8192, 128, args.steps, args.warmup, peaks, seed=3,
+                                 scale_in=0.5, want_lse=False)
+        elif name == "decode_c4":
+            res, _ = run_decode(torch, low, ffi, dev, name, 64, 32, 8, 128, 16, 512, 8192, 40000, args.steps, args.warmup,
+                                peaks, seed=4)
+        elif name == "decode_c4_small":    # 16 sequences, 12k-page pool (0.8 GB of cache): same kernel
+            res, _ = run_decode(torch, low, ffi, dev, name, 16, 32, 8, 128, 16, 512, 8192, 12000, args.steps, args.warmup,
+                                peaks, seed=4)
+        elif name == "decode_c5":
+            res, _ = run_decode(torch, low, ffi, dev, name, 256, 64, 8, 128, 16, 1024, 32768, None, args.steps, args.warmup,
+                                peaks, seed=5)
+        else:
+            raise SystemExit(f"unknown --profile {name}")
+        print(json.dumps(res))
+        return
 
     sampler = ClockSampler(local_rank)
     workloads = {}

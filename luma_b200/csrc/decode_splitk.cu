@@ -140,9 +140,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
     const int g = lane >> 2;   // mma row group
     const int c4 = lane & 3;
 
-    const int split = blockIdx.x;
-    const int kvh = blockIdx.y / a.head_blocks;
-    const int hb = blockIdx.y - kvh * a.head_blocks;
+    // KV heads vary fastest across the grid: the CTAs that read the adjacent 256-byte slices of the
+    // same token rows (one slice per KV head) are launched together, which keeps DRAM pages open.
+    const int kvh = blockIdx.x / a.head_blocks;
+    const int hb = blockIdx.x - kvh * a.head_blocks;
+    const int split = blockIdx.y;
     const int s = blockIdx.z;
 
     const int L = a.context_lens[s];
@@ -184,29 +186,34 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
     const int n_tiles = (chunk_end - chunk_begin + kTile - 1) / kTile;   // tiles in the chunk
     const int my_tiles = (n_tiles - warp + kWarps - 1) / kWarps;         // tiles warp takes: warp, warp+4, ...
 
-    // one lane moves half a row (8 or 4 chunks) of K and of V for token row lane/2
-    const int cp_row = lane >> 1;
-    const int cp_half = lane & 1;
+    // Copies of one tile: a K/V row (D*2 bytes) is moved by kChunksPerRow adjacent lanes, 16 bytes
+    // each, so one warp instruction reads whole rows (full 128-byte lines). Lane r < 16 looks up the
+    // slot of token row r once per tile; the other lanes get it by shuffle.
+    constexpr int kRowsPerInstr = 32 / kChunksPerRow;      // 2 (D=128) or 4 (D=64)
+    constexpr int kInstrPerTile = kTile / kRowsPerInstr;   // 8 or 4
+    static_assert(kCopiesPerLane == kInstrPerTile, "a lane issues one 16-byte copy per instruction");
+    const int cp_ch = lane % kChunksPerRow;
+    const int cp_sub = lane / kChunksPerRow;
     auto issue = [&](int it) {
         if (it < my_tiles) {
             const int tile = warp + it * kWarps;
-            const int j = chunk_begin + tile * kTile + cp_row;
-            const bool valid = j < chunk_end;
-            long long off = 0;
-            if (valid) {
+            const int j = chunk_begin + tile * kTile + (lane & 15);
+            long long my_off = -1;   // element offset of token row (lane & 15), -1 when past the chunk
+            if (j < chunk_end) {
                 const int slot = block_slot(a.block_tables, s, a.max_blocks, j, a.block_size);
-                off = (long long)slot * kv_pitch + (long long)kvh * D;
+                my_off = (long long)slot * kv_pitch + (long long)kvh * D;
             }
             unsigned char* kst = ring + (it % kStages) * S::kStageBytes;
             unsigned char* vst = kst + S::kTileBytes;
-            const T* ksrc = kg + off;
-            const T* vsrc = vg + off;
 #pragma unroll
-            for (int i = 0; i < kCopiesPerLane; ++i) {
-                const int ch = cp_half * kCopiesPerLane + i;
-                const int dst = cp_row * S::kRowBytes + ((ch ^ (cp_row & 7)) << 4);
-                cp_async_16(kst + dst, ksrc + ch * 8, valid);
-                cp_async_16(vst + dst, vsrc + ch * 8, valid);
+            for (int i = 0; i < kInstrPerTile; ++i) {
+                const int row = i * kRowsPerInstr + cp_sub;
+                const long long off = __shfl_sync(0xffffffffu, my_off, row);
+                const bool valid = off >= 0;
+                const long long src = (valid ? off : 0) + cp_ch * 8;
+                const int dst = row * S::kRowBytes + ((cp_ch ^ (row & 7)) << 4);
+                cp_async_16(kst + dst, kg + src, valid);
+                cp_async_16(vst + dst, vg + src, valid);
             }
         }
         cp_async_commit();  // committed even when empty so that group counting stays uniform
@@ -440,7 +447,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         cudaGetLastError();
         return FLASH_ATTN_ERR_CUDA;
     }
-    dim3 grid(max_splits, p.kv_heads * head_blocks, p.num_seqs);
+    dim3 grid(p.kv_heads * head_blocks, max_splits, p.num_seqs);
     decode_splitk_kernel<T, D><<<grid, kThreads, S::kBytes, stream>>>(a);
     int rc = check_launch("decode_splitk_kernel");
     if (rc != FLASH_ATTN_OK) return rc;
@@ -581,7 +588,7 @@ int launch_static(const void* q, const void* k, const void* v, void* o, const in
         cudaGetLastError();
         return FLASH_ATTN_ERR_CUDA;
     }
-    dim3 grid(max_splits, kv_heads * head_blocks, num_seqs);
+    dim3 grid(kv_heads * head_blocks, max_splits, num_seqs);
     decode_splitk_kernel<T, D><<<grid, kThreads, S::kBytes, stream>>>(a);
     int rc = check_launch("decode_splitk_kernel");
     if (rc != FLASH_ATTN_OK) return rc;
