@@ -207,6 +207,7 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *   flash_attn_last_launches  : number of kernels that call launched.
  *   flash_attn_set_option     : named integer knobs (returns 0 if the name is known):
  *       "force_generic"       1 = route everything through the SIMT tile kernel
+ *       "prefill_trace"       1 = record the timeline read by flash_attn_debug_read
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  */
 /*
@@ -217,6 +218,14 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  */
 const char* flash_attn_version(void);
 int flash_attn_device_status(void);
+/*
+ *   flash_attn_debug_read     : copies up to `bytes` (max 65536) of the current device's debug
+ *                               area to host memory: int status word at byte 0; from byte 256,
+ *                               when the option "prefill_trace" is 1, clock64 stamps of one CTA of
+ *                               the last tcgen05 prefill launch, laid out [role 0..2][kv step
+ *                               0..59][event 0..7] as int64. Returns bytes copied or -1.
+ */
+int flash_attn_debug_read(void* dst, int bytes);
 const char* flash_attn_last_path(void);
 int flash_attn_last_launches(void);
 int flash_attn_set_option(const char* name, int value);

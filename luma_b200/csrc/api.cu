@@ -21,6 +21,7 @@ thread_local const char* g_last_path = "";
 thread_local int g_last_launches = 0;
 int g_force_generic = 0;
 int g_decode_chunk = 0;
+int g_prefill_trace = 0;
 }  // namespace
 
 void set_last_error(const char* msg) { std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
@@ -39,6 +40,7 @@ void note_path(const char* name, int launches) {
 
 int get_option_force_generic() { return g_force_generic; }
 int get_option_decode_chunk() { return g_decode_chunk; }
+int get_option_prefill_trace() { return g_prefill_trace; }
 
 int check_launch(const char* what) {
     const cudaError_t err = cudaGetLastError();
@@ -301,10 +303,19 @@ int flash_attn_device_status(void) {
     return fa::prefill_device_status();
 }
 
+int flash_attn_debug_read(void* dst, int bytes) {
+    if (!fa::have_device()) return -1;
+    return fa::prefill_debug_read(dst, bytes);
+}
+
 int flash_attn_set_option(const char* name, int value) {
     if (name == nullptr) return 1;
     if (std::strcmp(name, "force_generic") == 0) {
         fa::g_force_generic = value;
+        return 0;
+    }
+    if (std::strcmp(name, "prefill_trace") == 0) {
+        fa::g_prefill_trace = value;
         return 0;
     }
     if (std::strcmp(name, "decode_chunk_tokens") == 0) {

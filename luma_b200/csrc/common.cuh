@@ -112,6 +112,7 @@ void set_last_errorf(const char* fmt, ...);
 void note_path(const char* name, int launches);   // records flash_attn_last_path / _launches
 int get_option_force_generic();
 int get_option_decode_chunk();
+int get_option_prefill_trace();
 
 // Returns FLASH_ATTN_OK or FLASH_ATTN_ERR_CUDA (with last error set) after a launch.
 int check_launch(const char* what);
@@ -128,6 +129,9 @@ int launch_debug_block_slots(const int* block_tables, const int* context_lens, c
 // Reads and clears the per-device status word of the tcgen05 kernel (0 = every bounded wait was
 // satisfied; otherwise the code of the wait that expired). Synchronises the device.
 int prefill_device_status();
+// Copies the per-device debug area (status word, then from byte 256 the optional kernel timeline)
+// to host memory; returns the bytes copied or -1.
+int prefill_debug_read(void* dst, int bytes);
 
 // Split-K scratch of the decode path: one buffer per (device, stream), grown on demand.
 void* decode_workspace(cudaStream_t stream, size_t bytes);

@@ -63,6 +63,7 @@ struct PrefillArgs {
     void* o;
     float* lse;
     int* status;    // device word, set to non-zero when a bounded wait expired
+    long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
     float scale_log2;
 };
@@ -221,6 +222,12 @@ __device__ __forceinline__ unsigned make_idesc(bool b_mn_major) {
     return d;
 }
 
+// Timeline slots: role (0/1 = softmax warpgroup, 2 = MMA issuer) x kv step (< 60) x event (< 8).
+constexpr int kTraceSteps = 60;
+__device__ __forceinline__ void trace_event(long long* trace, int role, int j, int ev) {
+    if (trace != nullptr && j < kTraceSteps) trace[(role * kTraceSteps + j) * 8 + ev] = clock64();
+}
+
 struct TileInfo {
     int valid;    // this query tile exists
     int head;     // query head
@@ -284,6 +291,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sm.tmem_base;
+    // only the heaviest CTA of the first (batch, KV head) records its timeline, one thread per role
+    long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
 
     if (warp == kLoadWarp) {
         // ------------------------------ TMA producer ------------------------------
@@ -383,10 +392,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     if (j >= ts[t].n_kv) continue;
                     alive = mbar_wait(sm, &sm.p_full[t], (unsigned)j & 1u, a.status, 14 + t);
                     if (!alive) break;
+                    trace_event(trace, 2, j, t * 2);
                     tc_fence_after();
                     issue_pv(t, s, j > 0);
                     if (j + 1 < ts[t].n_kv) issue_s(t, s1);
                     tc_commit(&sm.s_full[t]);   // S_t(j+1) ready, or after the last PV: O_t final
+                    trace_event(trace, 2, j, t * 2 + 1);
                 }
                 if (!alive) break;
                 tc_commit(&sm.v_empty[s]);
@@ -410,30 +421,37 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         for (int j = 0; j < ti.n_kv && alive; ++j) {
             alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a.status, 20 + t));
             if (!alive) break;
+            trace_event(trace, t, j, 0);
             tc_fence_after();
-            float sv[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
-            tc_wait_ld();
-
             const int key0 = j * kBlockN;
             // mask only where the causal diagonal or the end of K/V cuts through this tile
             const long long limit_ll = min(pos, (long long)a.kv_seq_len - 1) - key0;
             const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)a.start_pos + ti.row0, (long long)a.kv_seq_len - 1);
-            if (need_mask) {
-                const int limit = (int)max(-1LL, min(limit_ll, (long long)kBlockN));
+            const int limit = need_mask ? (int)max(-1LL, min(limit_ll, (long long)kBlockN)) : kBlockN;
+
+            // Row of S: four 32-column loads; the running max of a chunk is folded while the next
+            // chunk is still in flight, with eight independent chains instead of one long one.
+            float sv[4][32];
+            float mx8[8];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+            for (int e = 0; e < 8; ++e) mx8[e] = -INFINITY;
+            tc_ld32(s_addr, sv[0]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tc_wait_ld();
+                if (c + 1 < 4) tc_ld32(s_addr + (c + 1) * 32, sv[c + 1]);
+                if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i > limit) sv[c][i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sv[c][i]);
             }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[c][i]);
+            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
+            trace_event(trace, t, j, 1);
 
             float alpha = 1.0f;
             bool changed = false;
@@ -456,7 +474,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             }
             const float m_use = (m == -INFINITY) ? 0.0f : m;
-            float sum = 0.0f;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 unsigned pu[32];
@@ -466,15 +484,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     const int ii = (i & 15) * 2;
                     const float p0 = ex2(fmaf(sv[cc][ii], a.scale_log2, -m_use));
                     const float p1 = ex2(fmaf(sv[cc][ii + 1], a.scale_log2, -m_use));
-                    sum += p0 + p1;
+                    sum4[i & 3] += p0 + p1;
                     pu[i] = pack16<T>(p0, p1);
                 }
                 tc_st32(s_addr + c * 32, pu);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
+            trace_event(trace, t, j, 2);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&sm.p_full[t]);
+            trace_event(trace, t, j, 3);
         }
 
         // epilogue: O_t is final once the commit after the last P.V has arrived
@@ -552,6 +573,8 @@ bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int se
     return rc == CUDA_SUCCESS;
 }
 
+// Per-device debug area: the status word, then (from byte 256) the optional timeline.
+constexpr size_t kDebugBytes = 65536;
 std::mutex g_status_mutex;
 int* g_status_word[64] = {nullptr};
 
@@ -561,11 +584,11 @@ int* status_word() {
     std::lock_guard<std::mutex> lock(g_status_mutex);
     if (g_status_word[dev] == nullptr) {
         int* p = nullptr;
-        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) {
+        if (cudaMalloc(&p, kDebugBytes) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
-        cudaMemset(p, 0, sizeof(int));
+        cudaMemset(p, 0, kDebugBytes);
         g_status_word[dev] = p;
     }
     return g_status_word[dev];
@@ -586,6 +609,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.o = p.o;
     a.lse = p.lse;
     a.status = status;
+    a.trace = get_option_prefill_trace() ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
     a.batch = p.num_seqs;
     a.q_seq_len = p.q_seq_len;
     a.kv_seq_len = p.kv_seq_len;
@@ -623,6 +647,17 @@ int prefill_device_status() {
     }
     if (h != 0) cudaMemset(status, 0, sizeof(int));
     return h;
+}
+
+int prefill_debug_read(void* dst, int bytes) {
+    int* status = status_word();
+    if (status == nullptr || dst == nullptr || bytes <= 0) return -1;
+    const size_t n = (size_t)bytes < kDebugBytes ? (size_t)bytes : kDebugBytes;
+    if (cudaMemcpy(dst, status, n, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return (int)n;
 }
 
 int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {

@@ -38,7 +38,7 @@ EXPORTED_SYMBOLS = (
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
     + ["flash_attn_decode_bf16_noalloc"]
-    + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_last_path",
+    + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
 
@@ -61,6 +61,8 @@ lib.flash_attn_version.argtypes = []
 lib.flash_attn_version.restype = c_char_p
 lib.flash_attn_device_status.argtypes = []
 lib.flash_attn_device_status.restype = c_int
+lib.flash_attn_debug_read.argtypes = [c_void_p, c_int]
+lib.flash_attn_debug_read.restype = c_int
 lib.flash_attn_last_path.argtypes = []
 lib.flash_attn_last_path.restype = c_char_p
 lib.flash_attn_last_launches.argtypes = []
