@@ -40,7 +40,7 @@ class HeadAllGather:
         self.world = dist.get_world_size(group)
         b, s, h, d = local_shape
         self.local_shape = tuple(local_shape)
-        self.staging = torch.empty((self.world, b * s, h * d), dtype=dtype, device=device)
+        self.staging = torch.empty((self.world * b * s, h * d), dtype=dtype, device=device)
         self.out = torch.empty((b, s, self.world * h, d), dtype=dtype, device=device)
         self.launches = 2  # the NCCL kernel and the interleaving copy
 
@@ -49,7 +49,7 @@ class HeadAllGather:
         b, s, h, d = self.local_shape
         dist.all_gather_into_tensor(self.staging, o_local.view(b * s, h * d), group=self.group)
         # (G, B*S, H*d) -> (B*S, G, H*d): one pass over the gathered data
-        self.out.view(b * s, self.world, h * d).copy_(self.staging.permute(1, 0, 2))
+        self.out.view(b * s, self.world, h * d).copy_(self.staging.view(self.world, b * s, h * d).permute(1, 0, 2))
         return self.out
 
 
