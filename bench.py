@@ -232,6 +232,112 @@ def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool
     return res, (q, kc, vc, o, lens_d, table_d)
 
 
+def _max_over_ranks(torch, dist, dev, sec):
+    if dist is None:
+        return sec
+    t = torch.tensor([sec], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, b, hq, hkv, s, d, steps, warmup, peaks, seed, chunks=4):
+    """Strong scaling: the (b, s, hq, d) problem is split by KV-head groups over `world` ranks; every
+    rank ends with the full O. The local work is cut into `chunks` row ranges (start_pos form of
+    the same entry point) so that the all-gather of one range overlaps the attention of the next."""
+    from luma_b200 import dist as fdist
+    qs, kvs = fdist.shard_heads(hq, hkv, world, rank)
+    hq_l, hkv_l = qs.stop - qs.start, kvs.stop - kvs.start
+    q, k, v = make_prefill(torch, dev, b, hq_l, hkv_l, s, d, seed + rank)
+    scale = 1.0 / math.sqrt(d)
+    assert b == 1 and s % chunks == 0
+    rows = s // chunks
+    o_local = torch.empty_like(q)
+    out = torch.empty(b, s, hq, d, device=dev, dtype=torch.bfloat16) if world > 1 else o_local
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    staging = [torch.empty(world * rows, hq_l * d, device=dev, dtype=torch.bfloat16) for _ in range(2)] if world > 1 else None
+    launches = [0]
+
+    def step():
+        launches[0] = 0
+        main = torch.cuda.current_stream()
+        for c in range(chunks):
+            r0 = c * rows
+            qc = q[:, r0:r0 + rows]
+            oc = o_local[:, r0:r0 + rows]
+            # rows [r0, r0+rows) see keys [0, r0+rows): the same op with start_pos = r0
+            low.flash_attn(qc, k, v, oc, b, rows, r0 + rows, hq_l, hkv_l, d, r0, scale)
+            launches[0] += ffi.last_launches()
+            if world > 1:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    st = staging[c & 1]
+                    dist.all_gather_into_tensor(st, oc.reshape(rows, hq_l * d))
+                    out[0, r0:r0 + rows].view(rows, world, hq_l * d).copy_(st.view(world, rows, hq_l * d).permute(1, 0, 2))
+                launches[0] += 2
+        if world > 1:
+            main.wait_stream(comm)
+
+    step()
+    path = ffi.last_path()
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, barrier))
+    flops = causal_flops(b, hq, s, s, d)
+    tf = flops * steps / sec / 1e12
+    peak = peaks["bf16_tflops"]
+    return {
+        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "per_gpu": tf / world,
+        "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
+        "launches_per_step": launches[0],
+        "config": {"workload": "prefill_c5", "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
+                   "causal": True, "flops_per_step": flops,
+                   "parallelism": f"KV-head groups over {world} GPU(s), {chunks} row chunks, all-gather of O overlapped"},
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s",
+                     "frac": tf / world / peak, "traffic": None,
+                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included",
+                     "frac_of_nominal_2250": tf / world / NOMINAL_TFLOPS},
+    }
+
+
+def run_sharded_decode(torch, low, ffi, dev, dist, world, rank, batch, hq, hkv, d, page, lo, hi, steps, warmup, peaks, seed):
+    """Strong scaling of paged decode: every rank holds the cache slice of its KV heads
+    (num_blocks, page, hkv/world, d); block tables and lengths are replicated; O is all-gathered."""
+    from luma_b200 import dist as fdist
+    qs, kvs = fdist.shard_heads(hq, hkv, world, rank)
+    hq_l, hkv_l = qs.stop - qs.start, kvs.stop - kvs.start
+    q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq_l, hkv_l, d, page, lo, hi, None, seed)
+    o_local = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    max_blocks = table_d.shape[1]
+    gather = fdist.HeadAllGather(dist.group.WORLD, (batch, 1, hq_l, d), torch.bfloat16, dev) if world > 1 else None
+
+    def step():
+        low.flash_attn_with_kvcache(q, kc, vc, o_local, table_d, lens_d, batch, 1, hq_l, hkv_l, d, page, max_blocks, scale)
+        if gather is not None:
+            gather(o_local)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches() + (2 if gather is not None else 0)
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, barrier))
+    nbytes = decode_bytes(lens, hq, hkv, d, page)   # whole job: all KV heads
+    gbs = nbytes * steps / sec / 1e9
+    peak = peaks["hbm_gbs"]
+    return {
+        "metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "per_gpu": gbs / world,
+        "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
+        "launches_per_step": launches,
+        "config": {"workload": "decode_c5", "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+                   "page_size": page, "context": [int(lo), int(hi)], "tokens": int(lens.sum()),
+                   "pool_pages": int(kc.shape[0]), "bytes_per_step": nbytes,
+                   "parallelism": f"KV heads over {world} GPU(s), all-gather of O"},
+        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth); per GPU, all-gather included",
+                     "frac_of_nominal_8000": gbs / world / NOMINAL_HBM_GBS},
+    }
+
+
 # ------------------------------------------------------------------------------------------
 # CPU baseline (oracle port of luma-cpu's math path) — bounded sample of the primary workload
 # ------------------------------------------------------------------------------------------
@@ -454,6 +560,18 @@ def main():
             workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,
                                                     40000, max(K, 20), 5, peaks, seed=4)
             del _b
+            torch.cuda.empty_cache()
+
+    # ---- BASELINE.json configs[4]: the head-sharded shape, total work fixed, split over N GPUs ----
+    if not args.small and only in (None, "prefill_c5", "decode_c5", "c5"):
+        extra_steps = max(3, min(K, 10))
+        if only in (None, "prefill_c5", "c5"):
+            workloads["prefill_c5"] = run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, 1, 64, 8, 16384, 128,
+                                                          extra_steps, 3, peaks, seed=50, chunks=4)
+            torch.cuda.empty_cache()
+        if only in (None, "decode_c5", "c5"):
+            workloads["decode_c5"] = run_sharded_decode(torch, low, ffi, dev, dist, world, rank, 256, 64, 8, 128, 16,
+                                                        1024, 32768, max(extra_steps, 10), 3, peaks, seed=51)
             torch.cuda.empty_cache()
 
     # ---- CPU baseline, rank 0, N == 1 only -----------------------------------------------------
