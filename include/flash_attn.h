@@ -158,6 +158,30 @@ int flash_attn_bf16_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, 
                         int head_size, int start_pos, float scale, const uint8_t* attn_mask, void* stream);
 
 /*
+ * Head-sharded causal prefill with the output all-gather fused into the kernel's epilogue. No
+ * counterpart in the reference (its luma-dist all_gather, luma-dist/src/backends/nccl/backend.rs:
+ * 167-180, is a separate collective with two layout copies and a memset around it).
+ *   q : (batch, q_seq_len, q_num_heads, 128) — this rank's query heads;  k, v : this rank's KV heads
+ *   o_peers : HOST array of n_peers device pointers, one per GPU of the group (this GPU's own
+ *             buffer included), each to the FULL output (batch, q_seq_len, q_heads_total, 128).
+ *             Peer buffers must be mapped into this process (CUDA IPC or symmetric memory).
+ *   The kernel stores its heads at head index q_head_offset of every buffer with ordinary 16-byte
+ *   stores (posted writes over NVLink for peers): no TMA towards peers, no multicast, no waiting
+ *   on peers inside the kernel. The caller synchronises the group (a barrier after the launch)
+ *   before anyone reads the gathered tensor. lse (optional) is local: (batch, q_num_heads, q_seq_len).
+ * f16/bf16, head_size 128, q_seq_len >= 16, scale > 0, 16-byte aligned buffers; otherwise
+ * INVALID_HEAD_SIZE / INVALID_SHAPE with a message.
+ */
+int flash_attn_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                             void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
+                             int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                             int head_size, int start_pos, float scale, void* stream);
+int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                              void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
+                              int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                              int head_size, int start_pos, float scale, void* stream);
+
+/*
  * Runs the device-side block_slot arithmetic of the paged kernels and writes, for every sequence
  * s and token j < context_lens[s], the physical token slot to out_slots[offsets[s] + j]
  * (offsets = exclusive prefix sum of context_lens, supplied by the caller, num_seqs entries).

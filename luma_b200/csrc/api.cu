@@ -237,6 +237,80 @@ int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
     return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Head-sharded prefill whose epilogue writes this rank's heads into the full output tensor of every
+// GPU of the group (peer pointers): the all-gather of luma-dist's Comm::all_gather is part of the
+// kernel. Only the tcgen05 path implements it.
+int allgather_impl(int dtype, const void* q, const void* k, const void* v, void* const* o_peers, int n_peers,
+                   int q_heads_total, int q_head_offset, float* lse, int batch, int q_seq_len, int kv_seq_len,
+                   int q_num_heads, int kv_num_heads, int head_size, int start_pos, float scale, void* stream) {
+    g_last_error[0] = '\0';
+    cudaGetLastError();
+    if (q == nullptr || k == nullptr || v == nullptr || o_peers == nullptr) {
+        set_last_error("flash_attn_allgather: q/k/v/o_peers must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (n_peers < 1 || n_peers > 8) {
+        set_last_error("flash_attn_allgather: n_peers must be in 1..8");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    for (int i = 0; i < n_peers; ++i) {
+        if (o_peers[i] == nullptr) {
+            set_last_error("flash_attn_allgather: every entry of o_peers must be a device pointer");
+            return FLASH_ATTN_ERR_NULL_PTR;
+        }
+    }
+    if (batch <= 0 || q_seq_len <= 0 || kv_seq_len <= 0 || q_num_heads <= 0 || kv_num_heads <= 0) {
+        set_last_error("flash_attn_allgather: shape parameters must be positive");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_num_heads % kv_num_heads != 0) {
+        set_last_error("flash_attn_allgather: q_num_heads must be a multiple of kv_num_heads (GQA)");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (q_head_offset < 0 || q_heads_total <= 0 || q_head_offset + q_num_heads > q_heads_total) {
+        set_last_error("flash_attn_allgather: q_head_offset + q_num_heads must lie inside q_heads_total");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (start_pos < 0) {
+        set_last_error("flash_attn_allgather: start_pos must be >= 0");
+        return FLASH_ATTN_ERR_INVALID_START_POS;
+    }
+    if (head_size != 128) {
+        set_last_error("flash_attn_allgather: only head_size 128 is implemented on the fused path");
+        return FLASH_ATTN_ERR_INVALID_HEAD_SIZE;
+    }
+    AttnParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o_peers[0]; p.lse = lse;
+    p.mode = MODE_BATCH;
+    p.dtype = dtype;
+    p.num_seqs = batch;
+    p.q_seq_len = q_seq_len;
+    p.kv_seq_len = kv_seq_len;
+    p.q_heads = q_num_heads;
+    p.kv_heads = kv_num_heads;
+    p.head_size = head_size;
+    p.start_pos = start_pos;
+    p.block_size = 1;
+    p.scale = scale;
+    for (int i = 0; i < n_peers; ++i) p.o_peers[i] = o_peers[i];
+    p.n_out = n_peers;
+    p.o_heads = q_heads_total;
+    p.o_head0 = q_head_offset;
+    if (!have_device()) return FLASH_ATTN_ERR_CUDA;
+    DeviceGuard guard(q);
+    if (!guard.ok) {
+        set_last_error("flash_attn_allgather: could not select the device that owns q");
+        return FLASH_ATTN_ERR_CUDA;
+    }
+    const int rc = launch_prefill_tcgen05(p, reinterpret_cast<cudaStream_t>(stream));
+    if (rc < 0) {
+        set_last_error("flash_attn_allgather: this shape is outside the fused tensor-core path (needs q_seq_len >= 16, "
+                       "scale > 0, 16-byte aligned buffers)");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    return rc;
+}
+
 int kvcache_impl(int dtype, const void* q, const void* k_cache, const void* v_cache, void* o,
                  const int* block_tables, const int* context_lens, int num_seqs, int q_seq_len,
                  int q_heads, int kv_heads, int head_size, int block_size, int max_blocks,
@@ -373,6 +447,21 @@ FA_DEFINE_KVCACHE(flash_attn_with_kvcache_f32, float, fa::DT_F32)
 FA_DEFINE_KVCACHE(flash_attn_with_kvcache_f16, flash_attn_f16_t, fa::DT_F16)
 FA_DEFINE_KVCACHE(flash_attn_with_kvcache_bf16, flash_attn_bf16_t, fa::DT_BF16)
 #undef FA_DEFINE_KVCACHE
+
+int flash_attn_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                             void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
+                             int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                             int start_pos, float scale, void* stream) {
+    return fa::allgather_impl(fa::DT_F16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, lse, batch, q_seq_len,
+                              kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream);
+}
+int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                              void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
+                              int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                              int start_pos, float scale, void* stream) {
+    return fa::allgather_impl(fa::DT_BF16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, lse, batch, q_seq_len,
+                              kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream);
+}
 
 int flash_attn_debug_block_slots(const int* block_tables, const int* context_lens, const int* offsets,
                                  int num_seqs, int block_size, int max_blocks, int* out_slots,

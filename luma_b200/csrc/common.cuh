@@ -46,6 +46,12 @@ struct AttnParams {
     int max_blocks;
     int paged;
     float scale;
+    // head-sharded output (tcgen05 prefill only): n_out > 0 replaces `o` by n_out buffers of
+    // (batch, q_seq_len, o_heads, head_size) that each receive this call's heads at o_head0
+    void* o_peers[8];
+    int n_out;
+    int o_heads;
+    int o_head0;
 };
 
 // Per-sequence extents. Query row i of the sequence sits at global position pos_off + i and

@@ -59,8 +59,15 @@ struct SharedStorage {
     volatile int abort_flag;
 };
 
+constexpr int kMaxPeers = 8;
+
 struct PrefillArgs {
-    void* o;
+    // Output: n_out buffers of (batch, q_seq_len, o_heads, 128), each receiving this launch's heads
+    // at head offset o_head0. n_out == 1 with o_heads == q_heads is the ordinary call; with n_out > 1
+    // the buffers are the same tensor on every GPU of a head-sharded group (peer memory over
+    // NVLink), which makes the output all-gather part of the epilogue.
+    void* o[kMaxPeers];
+    int n_out, o_heads, o_head0;
     float* lse;
     int* status;    // device word, set to non-zero when a bounded wait expired
     long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
@@ -505,21 +512,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const bool row_ok = row < a.q_seq_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            T* orow = static_cast<T*>(a.o) + (((long long)b * a.q_seq_len + row) * a.q_heads + ti.head) * kD;
+            const long long o_off = (((long long)b * a.q_seq_len + row) * a.o_heads + a.o_head0 + ti.head) * kD;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 float ov[32];
                 tc_ld32(o_addr + c * 32, ov);
                 tc_wait_ld();
                 if (row_ok) {
+                    uint4 w[4];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 w;
-                        w.x = pack16<T>(ov[i] * inv, ov[i + 1] * inv);
-                        w.y = pack16<T>(ov[i + 2] * inv, ov[i + 3] * inv);
-                        w.z = pack16<T>(ov[i + 4] * inv, ov[i + 5] * inv);
-                        w.w = pack16<T>(ov[i + 6] * inv, ov[i + 7] * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                    for (int i = 0; i < 4; ++i) {
+                        w[i].x = pack16<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv);
+                        w[i].y = pack16<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv);
+                        w[i].z = pack16<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
+                        w[i].w = pack16<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
+                    }
+                    // plain 16-byte stores; for a peer buffer they travel over NVLink as posted writes
+                    for (int pe = 0; pe < a.n_out; ++pe) {
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = w[i];
                     }
                 }
             }
@@ -606,7 +618,18 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     if (status == nullptr) return -1;
 
     PrefillArgs a{};
-    a.o = p.o;
+    if (p.n_out > 0) {
+        if (p.n_out > kMaxPeers) return -1;
+        for (int i = 0; i < p.n_out; ++i) a.o[i] = p.o_peers[i];
+        a.n_out = p.n_out;
+        a.o_heads = p.o_heads;
+        a.o_head0 = p.o_head0;
+    } else {
+        a.o[0] = p.o;
+        a.n_out = 1;
+        a.o_heads = p.q_heads;
+        a.o_head0 = 0;
+    }
     a.lse = p.lse;
     a.status = status;
     a.trace = get_option_prefill_trace() ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
@@ -666,8 +689,9 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     if (p.head_size != kD) return -1;
     if (!(p.scale > 0.0f)) return -1;
     if (p.q_seq_len < 16) return -1;   // a handful of rows is not worth a 128-row tile
-    const uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
-                            reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.o);
+    uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
+                      reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.o);
+    for (int i = 0; i < p.n_out && i < 8; ++i) align |= reinterpret_cast<uintptr_t>(p.o_peers[i]);
     if (align & 15) return -1;
     const long long pairs = ((long long)(p.q_heads / p.kv_heads) * ((p.q_seq_len + kBlockM - 1) / kBlockM) + 1) / 2;
     if (pairs > 65535) return -1;

@@ -58,3 +58,58 @@ def all_gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
     group = group if group is not None else dist.group.WORLD
     g = HeadAllGather(group, o_local.shape, o_local.dtype, o_local.device)
     return g(o_local.contiguous())
+
+
+class PeerOutput:
+    """The full attention output (B, S, Hq_total, d), allocated on every rank and mapped into every
+    other rank of the group through CUDA IPC, so that a kernel on one GPU can store its heads
+    straight into all copies (plain stores over NVLink; nothing here uses TMA or multicast).
+
+    `fused_attention` runs the head-sharded prefill with the gather fused into its epilogue and
+    then synchronises the group, after which `self.out` holds every rank's heads.
+    """
+
+    def __init__(self, group, shape, dtype, device):
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.out = torch.empty(shape, dtype=dtype, device=device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, reduce_tensor(self.out), group=group)
+        self.peers = []          # keeps the mappings alive
+        self.ptrs = []
+        for r, (fn, args) in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.out.data_ptr())
+                continue
+            args = list(args)
+            args[6] = device.index if isinstance(device, torch.device) else int(device)  # map on MY device
+            t = fn(*args)
+            self.peers.append(t)
+            self.ptrs.append(t.data_ptr())
+        self._flag = torch.zeros(1, device=device)
+        dist.barrier(group=group)
+
+    def fused_attention(self, q, k, v, q_heads_total, q_head_offset, start_pos=0, scale=None, row0=0, lse=None):
+        """q (B, Sq, Hq_local, d), k/v (B, Skv, Hkv_local, d): this rank's shard. Writes rows
+        [row0, row0 + Sq) of every rank's output. Call `sync()` before reading `self.out`."""
+        from . import low
+        b, sq, hq_l, d = q.shape
+        skv, hkv_l = k.shape[1], k.shape[2]
+        scale = float(scale) if scale is not None else 1.0 / (d ** 0.5)
+        s_total = self.out.shape[1]
+        assert b == self.out.shape[0] and (row0 == 0 or b == 1)
+        esz = self.out.element_size()
+        off = row0 * q_heads_total * d * esz
+        # with row0 > 0 (b == 1) the call addresses a row range of the output; the kernel's batch
+        # stride then never matters because batch == 1
+        ptrs = [p + off for p in self.ptrs]
+        assert sq + row0 <= s_total
+        low.flash_attn_allgather(q, k, v, ptrs, q_heads_total, q_head_offset, b, sq, skv, hq_l, hkv_l, d,
+                                 int(start_pos), scale, None, lse)
+
+    def sync(self):
+        """Every rank's stores have landed everywhere once all ranks passed this point."""
+        dist.all_reduce(self._flag, group=self.group)
+        return self.out

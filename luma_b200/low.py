@@ -132,3 +132,25 @@ def debug_block_slots(block_tables, context_lens, offsets, num_seqs, block_size,
         _ptr(block_tables), _ptr(context_lens), _ptr(offsets), num_seqs, block_size, max_blocks,
         _ptr(out_slots), _stream_ptr(stream, block_tables))
     E.from_status(code, ffi.last_error())
+
+
+def flash_attn_allgather(q, k, v, o_peer_ptrs, q_heads_total, q_head_offset, batch, q_seq_len, kv_seq_len,
+                         q_num_heads, kv_num_heads, head_size, start_pos, scale, stream=None, lse=None) -> None:
+    """Head-sharded prefill whose epilogue stores this rank's heads into the full output buffer of
+    every GPU of the group (`o_peer_ptrs`: device pointers, own buffer included). Additive; the
+    reference runs attention and luma-dist's all_gather as two separate steps."""
+    import ctypes
+    sfx = _suffix(q)
+    if sfx == "f32":
+        raise E.Unsupported("flash_attn_allgather: f16/bf16 only")
+    q_need = batch * q_seq_len * q_num_heads * head_size
+    kv_need = batch * kv_seq_len * kv_num_heads * head_size
+    _check_len("q", q.numel(), q_need)
+    _check_len("k", k.numel(), kv_need)
+    _check_len("v", v.numel(), kv_need)
+    n = len(o_peer_ptrs)
+    arr = (ctypes.c_void_p * n)(*[int(p) for p in o_peer_ptrs])
+    code = getattr(ffi.lib, f"flash_attn_{sfx}_allgather")(
+        _ptr(q), _ptr(k), _ptr(v), ctypes.cast(arr, ctypes.c_void_p), n, q_heads_total, q_head_offset, _ptr(lse),
+        batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
