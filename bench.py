@@ -242,47 +242,33 @@ def _max_over_ranks(torch, dist, dev, sec):
 
 def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, b, hq, hkv, s, d, steps, warmup, peaks, seed, chunks=4):
     """Strong scaling: the (b, s, hq, d) problem is split by KV-head groups over `world` ranks; every
-    rank ends with the full O. The local work is cut into `chunks` row ranges (start_pos form of
-    the same entry point) so that the all-gather of one range overlaps the attention of the next."""
+    rank ends with the full O (the kernel stores its heads into every rank's output buffer)."""
     from luma_b200 import dist as fdist
     qs, kvs = fdist.shard_heads(hq, hkv, world, rank)
     hq_l, hkv_l = qs.stop - qs.start, kvs.stop - kvs.start
     q, k, v = make_prefill(torch, dev, b, hq_l, hkv_l, s, d, seed + rank)
     scale = 1.0 / math.sqrt(d)
-    assert b == 1 and s % chunks == 0
-    rows = s // chunks
-    o_local = torch.empty_like(q)
-    out = torch.empty(b, s, hq, d, device=dev, dtype=torch.bfloat16) if world > 1 else o_local
-    comm = torch.cuda.Stream(device=dev) if world > 1 else None
-    staging = [torch.empty(world * rows, hq_l * d, device=dev, dtype=torch.bfloat16) for _ in range(2)] if world > 1 else None
     launches = [0]
+    if world > 1:
+        peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
 
-    def step():
-        launches[0] = 0
-        main = torch.cuda.current_stream()
-        for c in range(chunks):
-            r0 = c * rows
-            qc = q[:, r0:r0 + rows]
-            oc = o_local[:, r0:r0 + rows]
-            # rows [r0, r0+rows) see keys [0, r0+rows): the same op with start_pos = r0
-            low.flash_attn(qc, k, v, oc, b, rows, r0 + rows, hq_l, hkv_l, d, r0, scale)
-            launches[0] += ffi.last_launches()
-            if world > 1:
-                ev = torch.cuda.Event()
-                ev.record(main)
-                comm.wait_event(ev)
-                with torch.cuda.stream(comm):
-                    st = staging[c & 1]
-                    dist.all_gather_into_tensor(st, oc.reshape(rows, hq_l * d))
-                    out[0, r0:r0 + rows].view(rows, world, hq_l * d).copy_(st.view(world, rows, hq_l * d).permute(1, 0, 2))
-                launches[0] += 2
-        if world > 1:
-            main.wait_stream(comm)
+        def step():
+            peer.fused_attention(q, k, v, hq, qs.start, scale=scale)
+            peer.sync()
+            launches[0] = 2
+    else:
+        o_local = torch.empty_like(q)
+
+        def step():
+            low.flash_attn(q, k, v, o_local, b, s, s, hq_l, hkv_l, d, 0, scale)
+            launches[0] = ffi.last_launches()
 
     step()
     path = ffi.last_path()
     barrier = (lambda: dist.barrier()) if dist is not None else None
     sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, barrier))
+    if world > 1:
+        peer.close()
     flops = causal_flops(b, hq, s, s, d)
     tf = flops * steps / sec / 1e12
     peak = peaks["bf16_tflops"]
@@ -292,7 +278,8 @@ def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, b, hq, hkv, s, 
         "launches_per_step": launches[0],
         "config": {"workload": "prefill_c5", "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
                    "causal": True, "flops_per_step": flops,
-                   "parallelism": f"KV-head groups over {world} GPU(s), {chunks} row chunks, all-gather of O overlapped"},
+                   "parallelism": f"KV-head groups over {world} GPU(s); all-gather of O fused into the kernel epilogue "
+                                  "(peer stores over NVLink) + one 4-byte all-reduce"},
         "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s",
                      "frac": tf / world / peak, "traffic": None,
                      "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included",
@@ -488,17 +475,18 @@ def main():
     else:
         from luma_b200 import dist as fdist
         q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed=2 + rank)
-        o_local = torch.empty_like(q)
         lse = torch.empty(b, hq, s, device=dev, dtype=torch.float32)
-        gather = fdist.HeadAllGather(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
-        scale = 1.0 / math.sqrt(d)
+        # the kernel's epilogue stores this rank's heads into every rank's full output (peer memory
+        # over NVLink); one tiny all-reduce then tells everyone that all stores have landed
+        peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq * world, d), torch.bfloat16, dev)
+        o_local = peer.out
 
         def step():
-            low.flash_attn(q, k, v, o_local, b, s, s, hq, hkv, d, 0, scale, None, None, lse)
-            gather(o_local)
+            peer.fused_attention(q, k, v, hq * world, hq * rank, lse=lse)
+            peer.sync()
 
         step()
-        path, launches = ffi.last_path(), ffi.last_launches() + gather.launches
+        path, launches = ffi.last_path(), ffi.last_launches() + 1
         sampler.start()
         sec = time_steps(torch, step, K, W, barrier)
         clocks = sampler.stop()
@@ -512,7 +500,8 @@ def main():
             "kernel_path": path, "launches_per_step": launches,
             "config": {"workload": "prefill_c2", "batch": b, "q_heads": hq * world, "kv_heads": hkv * world,
                        "seq_len": s, "head_dim": d, "causal": True, "lse": True, "flops_per_step": flops,
-                       "parallelism": f"head-sharded x{world} (32 heads per GPU) + one all-gather of O along heads",
+                       "parallelism": f"head-sharded x{world} (32 heads per GPU); the all-gather of O along heads is fused "
+                                      "into the kernel epilogue (peer stores over NVLink) + one 4-byte all-reduce",
                        "l2_policy": "inputs larger than L2"},
             "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": tf / world / peaks["bf16_tflops"], "traffic": None,
@@ -547,6 +536,8 @@ def main():
     del hq_h, hk_h, hv_h, ho
 
     # ---- the other BASELINE.json configs ------------------------------------------------------
+    if world > 1:
+        peer.close()
     del q, k, v, o, lse
     torch.cuda.empty_cache()
     if world == 1 and not args.small:

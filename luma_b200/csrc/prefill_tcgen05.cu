@@ -436,27 +436,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)a.start_pos + ti.row0, (long long)a.kv_seq_len - 1);
             const int limit = need_mask ? (int)max(-1LL, min(limit_ll, (long long)kBlockN)) : kBlockN;
 
-            // Row of S: four 32-column loads; the running max of a chunk is folded while the next
-            // chunk is still in flight, with eight independent chains instead of one long one.
             float sv[4][32];
-            float mx8[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) mx8[e] = -INFINITY;
-            tc_ld32(s_addr, sv[0]);
+            for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
+            tc_wait_ld();
+            if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                tc_wait_ld();
-                if (c + 1 < 4) tc_ld32(s_addr + (c + 1) * 32, sv[c + 1]);
-                if (need_mask) {
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i > limit) sv[c][i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sv[c][i]);
             }
-            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[c][i]);
             mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
             trace_event(trace, t, j, 1);
 
@@ -512,26 +507,62 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const bool row_ok = row < a.q_seq_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const long long o_off = (((long long)b * a.q_seq_len + row) * a.o_heads + a.o_head0 + ti.head) * kD;
+            if (a.n_out == 1) {
+                // single output: each thread stores its own row straight from registers
+                T* orow = static_cast<T*>(a.o[0]) + (((long long)b * a.q_seq_len + row) * a.o_heads + a.o_head0 + ti.head) * kD;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float ov[32];
-                tc_ld32(o_addr + c * 32, ov);
-                tc_wait_ld();
-                if (row_ok) {
-                    uint4 w[4];
+                for (int c = 0; c < 4; ++c) {
+                    float ov[32];
+                    tc_ld32(o_addr + c * 32, ov);
+                    tc_wait_ld();
+                    if (row_ok) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        w[i].x = pack16<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv);
-                        w[i].y = pack16<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv);
-                        w[i].z = pack16<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
-                        w[i].w = pack16<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = pack16<T>(ov[i] * inv, ov[i + 1] * inv);
+                            w.y = pack16<T>(ov[i + 2] * inv, ov[i + 3] * inv);
+                            w.z = pack16<T>(ov[i + 4] * inv, ov[i + 5] * inv);
+                            w.w = pack16<T>(ov[i + 6] * inv, ov[i + 7] * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                        }
                     }
-                    // plain 16-byte stores; for a peer buffer they travel over NVLink as posted writes
-                    for (int pe = 0; pe < a.n_out; ++pe) {
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off + c * 32);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) dst[i] = w[i];
+                }
+            } else {
+                // Stage this warp's 32 rows (256 B each) in the Q tile's shared memory — every MMA that read
+                // Q_t has finished — so that the global stores are whole rows: 16 lanes x 16 B contiguous,
+                // two rows per instruction. That matters most for the peer copies, which cross NVLink.
+                unsigned char* stage = sm.q[t];
+    #pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    float ov[32];
+                    tc_ld32(o_addr + c * 32, ov);
+                    tc_wait_ld();
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack16<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv);
+                        w.y = pack16<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv);
+                        w.z = pack16<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
+                        w.w = pack16<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
+                        const int ch = c * 4 + i;   // 16-byte chunk of the row, XOR-swizzled against bank conflicts
+                        *reinterpret_cast<uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4)) = w;
+                    }
+                }
+                __syncwarp();
+                {
+                    const int ch = lane & 15;
+                    const int sub = lane >> 4;
+                    const int warp_row0 = (warp & 3) * 32;
+    #pragma unroll 4
+                    for (int it = 0; it < 16; ++it) {
+                        const int rr = warp_row0 + it * 2 + sub;
+                        const int grow = ti.row0 + rr;
+                        if (grow < a.q_seq_len) {
+                            const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * 256 + ((ch ^ (rr & 15)) << 4));
+                            const long long o_off = (((long long)b * a.q_seq_len + grow) * a.o_heads + a.o_head0 + ti.head) * kD + ch * 8;
+                            for (int pe = 0; pe < a.n_out; ++pe)
+                                *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
+                        }
                     }
                 }
             }

@@ -113,3 +113,13 @@ class PeerOutput:
         """Every rank's stores have landed everywhere once all ranks passed this point."""
         dist.all_reduce(self._flag, group=self.group)
         return self.out
+
+    def close(self):
+        """Drops the mappings of the peers' buffers. Collective: every rank calls it, after which no
+        rank touches another rank's buffer again, so the owners may free them in any order."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.peers.clear()
+        self.ptrs = [self.out.data_ptr()]
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
