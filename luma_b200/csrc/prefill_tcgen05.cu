@@ -261,6 +261,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                        const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
     extern __shared__ unsigned char smem_raw[];
     SharedStorage& sm = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const long long t_entry = clock64();
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -274,7 +275,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const TileInfo t1 = tile_info(a, pair, 1, kvh, group, num_mb);
     const int n_max = max(t0.n_kv, t1.n_kv);
 
-    if (threadIdx.x == 0) {
+    // The producer thread initialises the barriers itself and issues the first loads right away (Q,
+    // and the K/V tiles that fill the empty ring), before the CTA-wide set-up barrier: the copies
+    // then fly while tensor memory is being allocated and the other warps start up.
+    const int n_pre = min(kStages, n_max);
+    if (warp == kLoadWarp && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&q_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&k_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&v_map) : "memory");
         sm.abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sm.q_full[i], 1);
@@ -289,6 +297,25 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        auto load_q = [&](const TileInfo& ti, int t) {
+            if (!ti.valid) return;
+            mbar_expect_tx(&sm.q_full[t], kTileBytes);
+            tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ti.head, ti.row0, b);
+            tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, ti.row0, b);
+        };
+        auto load_kv = [&](unsigned char* dst, const CUtensorMap* map, unsigned long long* bar, int j) {
+            mbar_expect_tx(bar, kTileBytes);
+            tma_load_4d(dst, map, bar, 0, kvh, j * kBlockN, b);
+            tma_load_4d(dst + kHalfBytes, map, bar, 64, kvh, j * kBlockN, b);
+        };
+        load_q(t0, 0);
+        if (n_pre > 0) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
+        load_q(t1, 1);
+        if (n_pre > 0) load_kv(sm.v[0], &v_map, &sm.v_full[0], 0);
+        for (int j = 1; j < n_pre; ++j) {
+            load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
+            load_kv(sm.v[j], &v_map, &sm.v_full[j], j);
+        }
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(smem_u32(&sm.tmem_base)) : "memory");
@@ -300,19 +327,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const unsigned tmem = sm.tmem_base;
     // only the heaviest CTA of the first (batch, KV head) records its timeline, one thread per role
     long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
+    // slot kTraceSteps - 1 of each role holds the CTA's life cycle instead of a kv step
+    if (trace != nullptr && warp == kMmaWarp) {
+        trace[(2 * kTraceSteps + kTraceSteps - 1) * 8 + 0] = t_entry;
+        trace_event(trace, 2, kTraceSteps - 1, 1);   // set-up (barriers, tensor memory) done
+    }
 
     if (warp == kLoadWarp) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             const TileInfo ts[2] = {t0, t1};
-            for (int t = 0; t < 2; ++t) {
-                if (!ts[t].valid) continue;
-                mbar_expect_tx(&sm.q_full[t], kTileBytes);
-                tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ts[t].head, ts[t].row0, b);
-                tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ts[t].head, ts[t].row0, b);
-            }
             bool alive = true;
-            for (int j = 0; j < n_max && alive; ++j) {
+            for (int j = n_pre; j < n_max && alive; ++j) {   // tiles 0 .. n_pre-1 were issued during set-up
                 const int s = j % kStages;
                 const unsigned ph = (unsigned)(j / kStages) & 1u;
                 alive = mbar_wait(sm, &sm.k_empty[s], ph ^ 1u, a.status, 1);
@@ -374,6 +400,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             for (int t = 0; t < 2 && alive; ++t)
                 if (ts[t].valid) alive = mbar_wait(sm, &sm.q_full[t], 0, a.status, 10);
             if (alive && n_max > 0) alive = mbar_wait(sm, &sm.k_full[0], 0, a.status, 11);
+            trace_event(trace, 2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
             if (alive && n_max > 0) {
                 tc_fence_after();
                 for (int t = 0; t < 2; ++t) {
@@ -570,11 +597,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 a.lse[((long long)b * a.q_heads + ti.head) * a.q_seq_len + row] =
                     l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
             }
+            trace_event(trace, t, kTraceSteps - 1, 0);       // epilogue stores issued
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    trace_event(trace, 2, kTraceSteps - 1, 3);               // every role done
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
