@@ -33,6 +33,12 @@ sys.path.insert(0, str(ROOT))
 
 NOMINAL_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from
+# the ncu captures summarised under profiles/. prefill_c2 was captured at full size; the decode
+# figure is the ratio measured on decode_c4_small (399.9 MB moved for 394.2 MB of algorithmic bytes,
+# L2 hit rate 0.4 %: traffic grows in proportion to the cached tokens) applied to the run's own bytes.
+NCU_TRAFFIC_BYTES = {"prefill_c2": 508_289_536 + 51_624_192}
+NCU_DECODE_TRAFFIC_RATIO = (394_140_672 + 5_787_136) / 394_223_184
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -198,7 +204,7 @@ def run_prefill(torch, low, ffi, dev, name, b, hq, hkv, s, d, steps, warmup, pea
                    "causal": True, "lse": want_lse, "flops_per_step": flops,
                    "l2_policy": "inputs larger than L2 (q+k+v+o = %d MiB)" % ((q.numel() * 2 + k.numel() * 4) * 2 // 2 ** 20 // 1)},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
-                     "traffic": None, "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
+                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
                      "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
     }
     return res, (q, k, v, o, lse)
@@ -226,7 +232,8 @@ def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool
                    "context": [int(lo), int(hi)], "tokens": int(lens.sum()), "pool_pages": int(kc.shape[0]),
                    "bytes_per_step": nbytes, "l2_policy": "K/V touched per step (%d MiB) larger than L2" % (nbytes // 2 ** 20)},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth)",
+                     "traffic": int(nbytes * NCU_DECODE_TRAFFIC_RATIO),
+                     "peak_source": f"of {peaks['source']} (copy bandwidth)",
                      "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS},
     }
     return res, (q, kc, vc, o, lens_d, table_d)
