@@ -68,6 +68,7 @@ struct PrefillArgs {
     // NVLink), which makes the output all-gather part of the epilogue.
     void* o[kMaxPeers];
     int n_out, o_heads, o_head0;
+    int staged_store;   // 1 = stage O rows in shared memory and store whole rows (always with n_out > 1)
     float* lse;
     int* status;    // device word, set to non-zero when a bounded wait expired
     long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
@@ -534,7 +535,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const bool row_ok = row < a.q_seq_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            if (a.n_out == 1) {
+            if (a.n_out == 1 && !a.staged_store) {
                 // single output: each thread stores its own row straight from registers
                 T* orow = static_cast<T*>(a.o[0]) + (((long long)b * a.q_seq_len + row) * a.o_heads + a.o_head0 + ti.head) * kD;
 #pragma unroll 1
@@ -692,7 +693,8 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     }
     a.lse = p.lse;
     a.status = status;
-    a.trace = get_option_prefill_trace() ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
+    a.staged_store = get_option_prefill_trace() == 2 ? 1 : 0;
+    a.trace = get_option_prefill_trace() == 1 ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
     a.batch = p.num_seqs;
     a.q_seq_len = p.q_seq_len;
     a.kv_seq_len = p.kv_seq_len;
