@@ -54,7 +54,8 @@ struct SharedStorage {
     unsigned long long k_full[kStages], k_empty[kStages];
     unsigned long long v_full[kStages], v_empty[kStages];
     unsigned long long s_full[2];   // MMA -> softmax: S_t ready (and every earlier MMA finished)
-    unsigned long long p_full[2];   // softmax -> MMA: P_t written, O_t rescaled
+    unsigned long long p_lo[2];     // softmax -> MMA: keys 0-63 of P_t written, O_t rescaled
+    unsigned long long p_hi[2];     // softmax -> MMA: keys 64-127 of P_t written
     unsigned int tmem_base;
     volatile int abort_flag;
 };
@@ -288,7 +289,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sm.q_full[i], 1);
             mbar_init(&sm.s_full[i], 1);
-            mbar_init(&sm.p_full[i], 128);
+            mbar_init(&sm.p_lo[i], 128);
+            mbar_init(&sm.p_hi[i], 128);
         }
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.k_full[i], 1);
@@ -388,12 +390,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                               kk > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int stage, bool accumulate) {
+            auto issue_pv = [&](int t, int stage, bool accumulate, int half) {
                 // O_t += P_t V : 8 K-steps of 16 keys; A = P from tensor memory (packed 16-bit, 8 columns
                 // per step), B = V MN-major: 64-column halves 16 KiB apart, 8-key groups 1 KiB apart
                 const unsigned vb = smem_u32(sm.v[stage]);
 #pragma unroll
-                for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
                     tc_mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, make_desc(vb + kk * 2048, kHalfBytes, 1024),
                               idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 }
@@ -425,11 +427,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (!alive) break;
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
-                    alive = mbar_wait(sm, &sm.p_full[t], (unsigned)j & 1u, a.status, 14 + t);
+                    // the first 64 keys of P_t arrive while the softmax still works on the other 64:
+                    // their half of P.V leaves the critical path
+                    alive = mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t);
                     if (!alive) break;
                     trace_event(trace, 2, j, t * 2);
                     tc_fence_after();
-                    issue_pv(t, s, j > 0);
+                    issue_pv(t, s, j > 0, 0);
+                    alive = mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_pv(t, s, true, 1);
                     if (j + 1 < ts[t].n_kv) issue_s(t, s1);
                     tc_commit(&sm.s_full[t]);   // S_t(j+1) ready, or after the last PV: O_t final
                     trace_event(trace, 2, j, t * 2 + 1);
@@ -518,13 +526,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     pu[i] = pack16<T>(p0, p1);
                 }
                 tc_st32(s_addr + c * 32, pu);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
+                if (c == 0) trace_event(trace, t, j, 2);
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
-            trace_event(trace, t, j, 2);
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(&sm.p_full[t]);
             trace_event(trace, t, j, 3);
         }
 
