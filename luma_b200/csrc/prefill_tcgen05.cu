@@ -74,6 +74,13 @@ struct PrefillArgs {
     int* status;    // device word, set to non-zero when a bounded wait expired
     long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
+    // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
+    int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
+    const int* cu_q;            // MODE_VARLEN: packed row offsets of q / o
+    const int* cu_k;            // MODE_VARLEN: packed row offsets (or, paged, lengths by difference) of k / v
+    const int* context_lens;    // MODE_KVCACHE: cached length per sequence, query tokens included
+    const int* block_tables;    // paged K/V: (batch, max_blocks) logical -> physical block
+    int paged, block_size, max_blocks;
     float scale_log2;
 };
 
@@ -244,17 +251,69 @@ struct TileInfo {
     int n_kv;     // K/V tiles it needs
 };
 
-__device__ __forceinline__ TileInfo tile_info(const PrefillArgs& a, int pair, int t, int kvh, int group, int num_mb) {
+// Extents of one sequence. Query row i sits at global position pos_off + i and sees keys
+// j < kv_len with j <= pos_off + i (bottom-right aligned for the varlen and kv-cache entry points).
+struct SeqExtent {
+    int q_len, kv_len, pos_off;
+    long long o_row0;     // first row of this sequence in o (rows of o_heads * 128 elements)
+    int q_crow, q_cb;     // TMA coordinates (row, batch) of the sequence's first q row
+    int kv_crow, kv_cb;   // same for contiguous K/V (unused when paged)
+};
+
+__device__ __forceinline__ SeqExtent seq_extent(const PrefillArgs& a, int s) {
+    SeqExtent e;
+    if (a.mode == MODE_BATCH) {
+        e.q_len = a.q_seq_len; e.kv_len = a.kv_seq_len; e.pos_off = a.start_pos;
+        e.o_row0 = (long long)s * a.q_seq_len;
+        e.q_crow = 0; e.q_cb = s; e.kv_crow = 0; e.kv_cb = s;
+    } else if (a.mode == MODE_VARLEN) {
+        const int q0 = a.cu_q[s], k0 = a.cu_k[s];
+        e.q_len = a.cu_q[s + 1] - q0; e.kv_len = a.cu_k[s + 1] - k0; e.pos_off = e.kv_len - e.q_len;
+        e.o_row0 = q0;
+        e.q_crow = q0; e.q_cb = 0; e.kv_crow = k0; e.kv_cb = 0;
+    } else {
+        e.q_len = a.q_seq_len; e.kv_len = a.context_lens[s]; e.pos_off = e.kv_len - e.q_len;
+        e.o_row0 = (long long)s * a.q_seq_len;
+        e.q_crow = 0; e.q_cb = s; e.kv_crow = 0; e.kv_cb = 0;
+    }
+    return e;
+}
+
+__device__ __forceinline__ TileInfo tile_info(const SeqExtent& a, int pair, int t, int kvh, int group, int num_mb) {
     TileInfo ti;
     const int idx = pair * 2 + t;
     ti.valid = idx < group * num_mb;
     const int mb = ti.valid ? idx / group : 0;
     ti.head = kvh * group + (ti.valid ? idx - mb * group : 0);
     ti.row0 = mb * kBlockM;
-    const int last_row = min(ti.row0 + kBlockM, a.q_seq_len) - 1;
-    const long long last_key = min((long long)a.kv_seq_len - 1, (long long)a.start_pos + last_row);
-    ti.n_kv = ti.valid ? (int)(last_key / kBlockN) + 1 : 0;
+    const int last_row = min(ti.row0 + kBlockM, a.q_len) - 1;
+    const long long last_key = min((long long)a.kv_len - 1, (long long)a.pos_off + last_row);
+    ti.n_kv = (ti.valid && last_key >= 0) ? (int)(last_key / kBlockN) + 1 : 0;   // 0: the tile sees no key at all
     return ti;
+}
+
+// One K or V tile (128 keys x 128 dims, two 64-column halves) of sequence s, tile index j.
+//   contiguous: two boxes of 128 rows starting at the sequence's row kv_crow + 128 j;
+//   paged     : one box per page and half (block_size rows), the page looked up in the block
+//               table; pages past the sequence's last one are requested at block -1, which is out
+//               of range for the tensor map and therefore arrives as zeros.
+__device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExtent& sq, int s, int kvh, unsigned char* dst,
+                                             const CUtensorMap* map, unsigned long long* bar, int j) {
+    mbar_expect_tx(bar, kTileBytes);
+    if (!a.paged) {
+        tma_load_4d(dst, map, bar, 0, kvh, sq.kv_crow + j * kBlockN, sq.kv_cb);
+        tma_load_4d(dst + kHalfBytes, map, bar, 64, kvh, sq.kv_crow + j * kBlockN, sq.kv_cb);
+    } else {
+        const int bs = a.block_size;
+        const int per_tile = kBlockN / bs;
+        const int n_pages = (sq.kv_len + bs - 1) / bs;
+        for (int i = 0; i < per_tile; ++i) {
+            const int pg = j * per_tile + i;
+            const int blk = pg < n_pages ? a.block_tables[(long long)s * a.max_blocks + pg] : -1;
+            tma_load_4d(dst + i * bs * 128, map, bar, 0, kvh, 0, blk);
+            tma_load_4d(dst + kHalfBytes + i * bs * 128, map, bar, 64, kvh, 0, blk);
+        }
+    }
 }
 
 template <typename T>
@@ -268,13 +327,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int group = a.q_heads / a.kv_heads;
-    const int num_mb = (a.q_seq_len + kBlockM - 1) / kBlockM;
+    const SeqExtent sq = seq_extent(a, blockIdx.x / a.kv_heads);
+    const int num_mb = (sq.q_len + kBlockM - 1) / kBlockM;
     const int kvh = blockIdx.x % a.kv_heads;
     const int b = blockIdx.x / a.kv_heads;
     const int pair = gridDim.y - 1 - blockIdx.y;   // heaviest (latest rows) first
 
-    const TileInfo t0 = tile_info(a, pair, 0, kvh, group, num_mb);
-    const TileInfo t1 = tile_info(a, pair, 1, kvh, group, num_mb);
+    const TileInfo t0 = tile_info(sq, pair, 0, kvh, group, num_mb);
+    const TileInfo t1 = tile_info(sq, pair, 1, kvh, group, num_mb);
+    if (!t0.valid && !t1.valid) return;   // this sequence is shorter than the grid's row range (whole CTA leaves)
     const int n_max = max(t0.n_kv, t1.n_kv);
 
     // The producer thread initialises the barriers itself and issues the first loads right away (Q,
@@ -303,13 +364,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         auto load_q = [&](const TileInfo& ti, int t) {
             if (!ti.valid) return;
             mbar_expect_tx(&sm.q_full[t], kTileBytes);
-            tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ti.head, ti.row0, b);
-            tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, ti.row0, b);
+            tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ti.head, sq.q_crow + ti.row0, sq.q_cb);
+            tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, sq.q_crow + ti.row0, sq.q_cb);
         };
         auto load_kv = [&](unsigned char* dst, const CUtensorMap* map, unsigned long long* bar, int j) {
-            mbar_expect_tx(bar, kTileBytes);
-            tma_load_4d(dst, map, bar, 0, kvh, j * kBlockN, b);
-            tma_load_4d(dst + kHalfBytes, map, bar, 64, kvh, j * kBlockN, b);
+            load_kv_tile(a, sq, b, kvh, dst, map, bar, j);
         };
         load_q(t0, 0);
         if (n_pre > 0) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
@@ -346,14 +405,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const unsigned ph = (unsigned)(j / kStages) & 1u;
                 alive = mbar_wait(sm, &sm.k_empty[s], ph ^ 1u, a.status, 1);
                 if (!alive) break;
-                mbar_expect_tx(&sm.k_full[s], kTileBytes);
-                tma_load_4d(sm.k[s], &k_map, &sm.k_full[s], 0, kvh, j * kBlockN, b);
-                tma_load_4d(sm.k[s] + kHalfBytes, &k_map, &sm.k_full[s], 64, kvh, j * kBlockN, b);
+                load_kv_tile(a, sq, b, kvh, sm.k[s], &k_map, &sm.k_full[s], j);
                 alive = mbar_wait(sm, &sm.v_empty[s], ph ^ 1u, a.status, 2);
                 if (!alive) break;
-                mbar_expect_tx(&sm.v_full[s], kTileBytes);
-                tma_load_4d(sm.v[s], &v_map, &sm.v_full[s], 0, kvh, j * kBlockN, b);
-                tma_load_4d(sm.v[s] + kHalfBytes, &v_map, &sm.v_full[s], 64, kvh, j * kBlockN, b);
+                load_kv_tile(a, sq, b, kvh, sm.v[s], &v_map, &sm.v_full[s], j);
             }
             // Make sure none of this CTA's bulk copies is still in flight when it exits: wait
             // (bounded) for the last fill of every stage and of the Q tiles.
@@ -456,7 +511,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const unsigned s_addr = tmem + lane_base + t * 128;
         const unsigned o_addr = tmem + lane_base + 256 + t * 128;
         const int row = ti.row0 + r;
-        const long long pos = (long long)a.start_pos + row;     // global position of this query row
+        const long long pos = (long long)sq.pos_off + row;      // global position of this query row
         float m = -INFINITY;   // reference max, log2 domain (may lag the true max by <= 2^8)
         float l = 0.0f;
         bool alive = true;
@@ -468,8 +523,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const int key0 = j * kBlockN;
             // mask only where the causal diagonal or the end of K/V cuts through this tile
-            const long long limit_ll = min(pos, (long long)a.kv_seq_len - 1) - key0;
-            const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)a.start_pos + ti.row0, (long long)a.kv_seq_len - 1);
+            const long long limit_ll = min(pos, (long long)sq.kv_len - 1) - key0;
+            const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)sq.pos_off + ti.row0, (long long)sq.kv_len - 1);
             const int limit = need_mask ? (int)max(-1LL, min(limit_ll, (long long)kBlockN)) : kBlockN;
 
             float sv[4][32];
@@ -541,16 +596,20 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a.status, 30 + t));
         if (alive && ti.valid) {
             tc_fence_after();
-            const bool row_ok = row < a.q_seq_len;
+            const bool row_ok = row < sq.q_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             if (a.n_out == 1 && !a.staged_store) {
                 // single output: each thread stores its own row straight from registers
-                T* orow = static_cast<T*>(a.o[0]) + (((long long)b * a.q_seq_len + row) * a.o_heads + a.o_head0 + ti.head) * kD;
+                T* orow = static_cast<T*>(a.o[0]) + ((sq.o_row0 + row) * a.o_heads + a.o_head0 + ti.head) * kD;
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
                     float ov[32];
                     tc_ld32(o_addr + c * 32, ov);
                     tc_wait_ld();
+                    if (ti.n_kv == 0) {   // the tile saw no key: tensor memory holds nothing of ours, the rows are zeros
+                    #pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = 0.0f;
+                    }
                     if (row_ok) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
@@ -573,6 +632,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     float ov[32];
                     tc_ld32(o_addr + c * 32, ov);
                     tc_wait_ld();
+                    if (ti.n_kv == 0) {   // the tile saw no key: tensor memory holds nothing of ours, the rows are zeros
+                    #pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = 0.0f;
+                    }
     #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 w;
@@ -593,9 +656,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     for (int it = 0; it < 16; ++it) {
                         const int rr = warp_row0 + it * 2 + sub;
                         const int grow = ti.row0 + rr;
-                        if (grow < a.q_seq_len) {
+                        if (grow < sq.q_len) {
                             const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * 256 + ((ch ^ (rr & 15)) << 4));
-                            const long long o_off = (((long long)b * a.q_seq_len + grow) * a.o_heads + a.o_head0 + ti.head) * kD + ch * 8;
+                            const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * kD + ch * 8;
                             for (int pe = 0; pe < a.n_out; ++pe)
                                 *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
                         }
@@ -654,6 +717,24 @@ bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int se
     return rc == CUDA_SUCCESS;
 }
 
+// Paged cache (num_blocks, block_size, heads, 128) viewed as 4-D {d, head, slot in block, block};
+// box = 64 x 1 x block_size x 1: one page of one head and one 64-column half per copy. The C ABI
+// does not say how many blocks the pool has, so the block extent is set far beyond any pool; only
+// block ids read from the table are ever requested (and -1 for "no page": out of range, zeros).
+bool encode_paged_map(CUtensorMap* map, const void* base, int dtype, int block_size, int heads) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)block_size, (cuuint64_t)1 << 30};
+    const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2, (cuuint64_t)block_size * heads * kD * 2};
+    if (strides[2] >= ((cuuint64_t)1 << 40)) return false;
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)block_size, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult rc = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
 // Per-device debug area: the status word, then (from byte 256) the optional timeline.
 constexpr size_t kDebugBytes = 65536;
 std::mutex g_status_mutex;
@@ -678,11 +759,15 @@ int* status_word() {
 template <typename T>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
     CUtensorMap qm, km, vm;
-    if (!encode_map(&qm, p.q, p.dtype, p.num_seqs, p.q_seq_len, p.q_heads) ||
-        !encode_map(&km, p.k, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads) ||
-        !encode_map(&vm, p.v, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads)) {
-        return -1;  // let the SIMT kernel take it
+    bool ok = encode_map(&qm, p.q, p.dtype, p.num_seqs, p.q_seq_len, p.q_heads);
+    if (p.paged) {
+        ok = ok && encode_paged_map(&km, p.k, p.dtype, p.block_size, p.kv_heads) &&
+             encode_paged_map(&vm, p.v, p.dtype, p.block_size, p.kv_heads);
+    } else {
+        ok = ok && encode_map(&km, p.k, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads) &&
+             encode_map(&vm, p.v, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads);
     }
+    if (!ok) return -1;  // let the SIMT kernel take it
     int* status = status_word();
     if (status == nullptr) return -1;
 
@@ -709,6 +794,14 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.q_heads = p.q_heads;
     a.kv_heads = p.kv_heads;
     a.start_pos = p.start_pos;
+    a.mode = p.mode;
+    a.cu_q = p.cu_q;
+    a.cu_k = p.cu_k;
+    a.context_lens = p.context_lens;
+    a.block_tables = p.block_tables;
+    a.paged = p.paged;
+    a.block_size = p.block_size;
+    a.max_blocks = p.max_blocks;
     a.scale_log2 = p.scale * 1.4426950408889634f;
 
     const int group = p.q_heads / p.kv_heads;
@@ -754,7 +847,16 @@ int prefill_debug_read(void* dst, int bytes) {
 }
 
 int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
-    if (p.mode != MODE_BATCH || p.mask != nullptr) return -1;
+    // batched entry point, and chunked prefill over a paged cache (whole pages must tile the 128-key
+    // K/V tile). The packed varlen entry point stays on the SIMT kernel: its C ABI carries no total
+    // row counts, so a tensor map with exact bounds cannot be built on the host.
+    if (p.mask != nullptr) return -1;
+    if (p.mode == MODE_KVCACHE) {
+        if (!p.paged || p.max_blocks <= 0) return -1;
+        if (p.block_size < 8 || p.block_size > 128 || (128 % p.block_size) != 0) return -1;
+    } else if (p.mode != MODE_BATCH) {
+        return -1;
+    }
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
     if (p.head_size != kD) return -1;
     if (!(p.scale > 0.0f)) return -1;
