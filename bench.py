@@ -239,6 +239,36 @@ def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool
     return res, (q, kc, vc, o, lens_d, table_d)
 
 
+def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, lo, hi, steps, warmup, peaks, seed):
+    """Chunked prefill: `sq` new tokens per sequence attend to a paged cache holding lo..hi tokens
+    (the new ones included), bottom-right causal; K/V pages are gathered by TMA through the block table."""
+    q1, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, None, seed)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed + 1)
+    q = torch.randn(batch, sq, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    max_blocks = table_d.shape[1]
+
+    def step():
+        low.flash_attn_with_kvcache(q, kc, vc, o, table_d, lens_d, batch, sq, hq, hkv, d, page, max_blocks, scale)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches()
+    sec = time_steps(torch, step, steps, warmup)
+    flops = sum(causal_flops(1, hq, sq, int(L), d, int(L) - sq) for L in lens)
+    tf = flops * steps / sec / 1e12
+    peak = peaks["bf16_tflops"]
+    return {
+        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+        "kernel_path": path, "launches_per_step": launches,
+        "config": {"workload": name, "batch": batch, "chunk": sq, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+                   "page_size": page, "context": [int(lo), int(hi)], "flops_per_step": flops},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)", "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
+    }
+
+
 def _max_over_ranks(torch, dist, dev, sec):
     if dist is None:
         return sec
@@ -553,6 +583,11 @@ def main():
             workloads["prefill_c3"], _b = run_prefill(torch, low, ffi, dev, "prefill_c3", 2, 32, 8, 8192, 128,
                                                       extra_steps, 3, peaks, seed=3, scale_in=0.5, want_lse=False)
             del _b
+            torch.cuda.empty_cache()
+        if only in (None, "paged_prefill"):
+            # the step before decode (not a BASELINE config): 1024-token chunks over paged contexts
+            workloads["paged_prefill"] = run_paged_prefill(torch, low, ffi, dev, "paged_prefill", 16, 1024, 32, 8, 128, 16,
+                                                           1024, 8192, extra_steps, 3, peaks, seed=6)
             torch.cuda.empty_cache()
         if only in (None, "decode_c4"):
             workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,

@@ -182,6 +182,21 @@ int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_
                               int head_size, int start_pos, float scale, void* stream);
 
 /*
+ * KV-cache append: the step before every paged decode / chunked prefill. No counterpart in the
+ * reference, which leaves writing the cache to the caller (src/api/high.rs:123-125).
+ *   k_new, v_new : (num_seqs, n_new, kv_heads, head_size) rows of the newly processed tokens
+ *   k_cache, v_cache : (num_blocks, block_size, kv_heads, head_size)
+ *   context_lens : (num_seqs) lengths AFTER the append; token t of sequence s goes to logical
+ *                  position context_lens[s] - n_new + t (positions < 0 are skipped), i.e. to slot
+ *                  block_tables[s*max_blocks + pos/block_size]*block_size + pos%block_size.
+ * Storage-type agnostic: elem_bytes is 2 (f16 / bf16) or 4 (f32); rows are copied bit for bit.
+ */
+int flash_attn_kvcache_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                              const int* block_tables, const int* context_lens, int num_seqs, int n_new,
+                              int kv_heads, int head_size, int elem_bytes, int block_size, int max_blocks,
+                              void* stream);
+
+/*
  * Runs the device-side block_slot arithmetic of the paged kernels and writes, for every sequence
  * s and token j < context_lens[s], the physical token slot to out_slots[offsets[s] + j]
  * (offsets = exclusive prefix sum of context_lens, supplied by the caller, num_seqs entries).

@@ -463,6 +463,35 @@ int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_
                               kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream);
 }
 
+int flash_attn_kvcache_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                              const int* block_tables, const int* context_lens, int num_seqs, int n_new,
+                              int kv_heads, int head_size, int elem_bytes, int block_size, int max_blocks,
+                              void* stream) {
+    fa::g_last_error[0] = '\0';
+    cudaGetLastError();
+    if (!k_new || !v_new || !k_cache || !v_cache || !block_tables || !context_lens) {
+        fa::set_last_error("flash_attn_kvcache_append: null pointer argument");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    if (num_seqs <= 0 || n_new <= 0 || kv_heads <= 0 || block_size <= 0 || max_blocks <= 0) {
+        fa::set_last_error("flash_attn_kvcache_append: num_seqs/n_new/kv_heads/block_size/max_blocks must be > 0");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (!fa::head_size_ok(head_size) || (elem_bytes != 2 && elem_bytes != 4)) {
+        fa::set_last_error("flash_attn_kvcache_append: head_size must be 32/64/128 and elem_bytes 2 or 4");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) | reinterpret_cast<uintptr_t>(k_cache) |
+         reinterpret_cast<uintptr_t>(v_cache)) & 15) {
+        fa::set_last_error("flash_attn_kvcache_append: buffers must be 16-byte aligned");
+        return FLASH_ATTN_ERR_INVALID_SHAPE;
+    }
+    if (!fa::have_device()) return FLASH_ATTN_ERR_CUDA;
+    fa::DeviceGuard guard(k_cache);
+    return fa::launch_kv_append(elem_bytes, k_new, v_new, k_cache, v_cache, block_tables, context_lens, num_seqs, n_new,
+                                kv_heads, head_size, block_size, max_blocks, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int flash_attn_debug_block_slots(const int* block_tables, const int* context_lens, const int* offsets,
                                  int num_seqs, int block_size, int max_blocks, int* out_slots,
                                  void* stream) {

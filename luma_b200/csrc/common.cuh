@@ -132,6 +132,10 @@ int launch_debug_block_slots(const int* block_tables, const int* context_lens, c
                              int num_seqs, int block_size, int max_blocks, int* out_slots,
                              cudaStream_t stream);
 
+int launch_kv_append(int elem_bytes, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                     const int* block_tables, const int* context_lens, int num_seqs, int n_new, int kv_heads,
+                     int head_size, int block_size, int max_blocks, cudaStream_t stream);
+
 // Reads and clears the per-device status word of the tcgen05 kernel (0 = every bounded wait was
 // satisfied; otherwise the code of the wait that expired). Synchronises the device.
 int prefill_device_status();

@@ -37,7 +37,8 @@ EXPORTED_SYMBOLS = (
     + [f"flash_attn_with_kvcache_{s}" for s in DTYPE_SUFFIX]
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
-    + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather"]
+    + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather",
+       "flash_attn_kvcache_append"]
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
@@ -60,6 +61,9 @@ for _s in ("f16", "bf16"):
                                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                           c_float, c_void_p]
     getattr(lib, f"flash_attn_{_s}_allgather").restype = c_int
+lib.flash_attn_kvcache_append.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+lib.flash_attn_kvcache_append.restype = c_int
 lib.flash_attn_last_error.argtypes = []
 lib.flash_attn_last_error.restype = c_char_p
 lib.flash_attn_version.argtypes = []

@@ -154,3 +154,18 @@ def flash_attn_allgather(q, k, v, o_peer_ptrs, q_heads_total, q_head_offset, bat
         _ptr(q), _ptr(k), _ptr(v), ctypes.cast(arr, ctypes.c_void_p), n, q_heads_total, q_head_offset, _ptr(lse),
         batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, _stream_ptr(stream, q))
     E.from_status(code, ffi.last_error())
+
+
+def kvcache_append(k_new, v_new, k_cache, v_cache, block_tables, context_lens, num_seqs, n_new, kv_heads,
+                   head_size, block_size, max_blocks, stream=None) -> None:
+    """Writes the K/V rows of the n_new newest tokens of every sequence into their pages
+    (`context_lens` = lengths after the append). Additive: the reference leaves this to the caller
+    (luma-flash-attn/src/api/high.rs:123-125)."""
+    need = num_seqs * n_new * kv_heads * head_size
+    _check_len("k_new", k_new.numel(), need)
+    _check_len("v_new", v_new.numel(), need)
+    code = ffi.lib.flash_attn_kvcache_append(
+        _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(context_lens),
+        num_seqs, n_new, kv_heads, head_size, k_new.element_size(), block_size, max_blocks,
+        _stream_ptr(stream, k_new))
+    E.from_status(code, ffi.last_error())
