@@ -269,6 +269,26 @@ def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, l
     }
 
 
+NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool (nominal 900)
+
+
+def fused_roofline(flops_per_gpu, nvlink_out_bytes_per_gpu, sec_per_step, peaks):
+    """Roofline of the fused attention + all-gather kernel, per GPU: the target time is the slower of
+    FLOPs / measured GEMM peak and bytes stored to peers over NVLink / measured peer bandwidth."""
+    t_math = flops_per_gpu / (peaks["bf16_tflops"] * 1e12)
+    t_link = nvlink_out_bytes_per_gpu / (NVLINK_PEER_GBS * 1e9)
+    if t_link > t_math:
+        gbs = nvlink_out_bytes_per_gpu / sec_per_step / 1e9
+        return {"bound": "nvlink", "achieved": gbs, "peak": NVLINK_PEER_GBS, "unit": "GB/s", "frac": gbs / NVLINK_PEER_GBS,
+                "traffic": None, "peak_source": "measured peer copy, per direction per GPU; bytes = this GPU's O shard "
+                                                "stored to every peer", "target_ms": t_link * 1e3}
+    tf = flops_per_gpu / sec_per_step / 1e12
+    return {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": tf / peaks["bf16_tflops"], "traffic": None,
+            "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included",
+            "frac_of_nominal_2250": tf / NOMINAL_TFLOPS, "target_ms": t_math * 1e3}
+
+
 def _max_over_ranks(torch, dist, dev, sec):
     if dist is None:
         return sec
@@ -317,10 +337,7 @@ def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, b, hq, hkv, s, 
                    "causal": True, "flops_per_step": flops,
                    "parallelism": f"KV-head groups over {world} GPU(s); all-gather of O fused into the kernel epilogue "
                                   "(peer stores over NVLink) + one 4-byte all-reduce"},
-        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s",
-                     "frac": tf / world / peak, "traffic": None,
-                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included",
-                     "frac_of_nominal_2250": tf / world / NOMINAL_TFLOPS},
+        "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks),
     }
 
 
@@ -540,9 +557,7 @@ def main():
                        "parallelism": f"head-sharded x{world} (32 heads per GPU); the all-gather of O along heads is fused "
                                       "into the kernel epilogue (peer stores over NVLink) + one 4-byte all-reduce",
                        "l2_policy": "inputs larger than L2"},
-            "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": tf / world / peaks["bf16_tflops"], "traffic": None,
-                         "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included"},
+            "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / K, peaks),
         }
         o = o_local
         scaling_note = "weak: 32 heads per GPU"
