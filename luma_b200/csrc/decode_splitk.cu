@@ -390,6 +390,19 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float* __restrict
     o[((long long)s * q_heads + h) * D + d] = from_f32<T>(acc * inv);
 }
 
+// Tokens per work item. A CTA needs several microseconds to fill its copy pipeline, so long
+// chunks win as long as there are enough of them: the largest of 4096/2048/1024 that still yields
+// >= 1500 work items (about 5 waves of 2 CTAs x 148 SMs, counted at the maximum length), else the
+// largest chunk >= 256 that yields at least 256. `base` = work items per split.
+static int auto_chunk(long long base, long long max_tokens) {
+    auto items = [&](int c) { return base * ((max_tokens + c - 1) / c); };
+    for (int c = 4096; c >= 1024; c >>= 1)
+        if (items(c) >= 1500) return c;
+    for (int c = 4096; c >= 256; c >>= 1)
+        if (items(c) >= 256) return c;
+    return 256;
+}
+
 template <typename T, int D>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
     using S = Smem<D>;
@@ -398,17 +411,9 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     const long long max_tokens = (long long)p.max_blocks * p.block_size;
     if (max_tokens <= 0) return -1;
 
-    // tokens per work item: 512 by default, halved while the grid cannot fill the machine,
-    // doubled while a sequence could need more than 32 splits
     const int unit = kWarps * kTile;
     int chunk = get_option_decode_chunk();
-    if (chunk <= 0) {
-        chunk = 512;
-        const long long base = (long long)p.num_seqs * p.kv_heads * head_blocks;
-        const long long want = 148LL * 2 * 4;
-        while (chunk > unit && base * ((max_tokens + chunk - 1) / chunk) < want) chunk >>= 1;
-        while ((max_tokens + chunk - 1) / chunk > 32) chunk <<= 1;
-    }
+    if (chunk <= 0) chunk = auto_chunk((long long)p.num_seqs * p.kv_heads * head_blocks, max_tokens);
     chunk = ((chunk + unit - 1) / unit) * unit;
     const long long max_splits_ll = (max_tokens + chunk - 1) / chunk;
     if (max_splits_ll > 65535 || p.num_seqs > 65535 || (long long)p.kv_heads * head_blocks > 65535) return -1;
@@ -544,11 +549,8 @@ int launch_static(const void* q, const void* k, const void* v, void* o, const in
                         rows1, kStaticScratchBytes, kStaticScratchBytes / row_bytes, D);
         return FLASH_ATTN_ERR_INVALID_SHAPE;
     }
-    long long chunk = 512;
+    long long chunk = auto_chunk((long long)num_seqs * kv_heads * head_blocks, max_tokens);
     {
-        const long long base = (long long)num_seqs * kv_heads * head_blocks;
-        const long long want = 148LL * 2 * 4;
-        while (chunk > unit && base * ((max_tokens + chunk - 1) / chunk) < want) chunk >>= 1;
         while (rows1 * (size_t)((max_tokens + chunk - 1) / chunk) * row_bytes > kStaticScratchBytes) chunk <<= 1;
     }
     chunk = ((chunk + unit - 1) / unit) * unit;
