@@ -199,6 +199,51 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Two f32 lanes in one 64-bit register for the packed FMA-pipe instructions of sm_100.
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for two finite x on the FMA pipe instead of the special-function unit: x = n + f with n the
+// nearest integer (magic-number rounding), a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5,
+// far below the 16-bit rounding of P), and n added to the exponent field. x is clamped at -126,
+// so the result is never below 2^-126 — callers use this only where no element is masked.
+__device__ __forceinline__ void ex2_fma2(float x0, float x1, float& p0, float& p1) {
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    const unsigned long long x2 = pack2(x0, x1);
+    const unsigned long long t2 = add2(x2, pack2(12582912.0f, 12582912.0f));   // 1.5 * 2^23
+    const unsigned long long n2 = add2(t2, pack2(-12582912.0f, -12582912.0f));
+    const unsigned long long f2 = fma2(n2, pack2(-1.0f, -1.0f), x2);
+    unsigned long long p2 = fma2(pack2(0.05517084f, 0.05517084f), f2, pack2(0.24260908f, 0.24260908f));
+    p2 = fma2(p2, f2, pack2(0.69326109f, 0.69326109f));
+    p2 = fma2(p2, f2, pack2(0.99992847f, 0.99992847f));
+    float t0, t1, q0, q1;
+    unpack2(t2, t0, t1);
+    unpack2(p2, q0, q1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 template <typename T> __device__ __forceinline__ unsigned pack16(float lo, float hi);
 template <> __device__ __forceinline__ unsigned pack16<__nv_bfloat16>(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -405,9 +450,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const unsigned ph = (unsigned)(j / kStages) & 1u;
                 alive = mbar_wait(sm, &sm.k_empty[s], ph ^ 1u, a.status, 1);
                 if (!alive) break;
+                trace_event(trace, 2, j, 6);
                 load_kv_tile(a, sq, b, kvh, sm.k[s], &k_map, &sm.k_full[s], j);
                 alive = mbar_wait(sm, &sm.v_empty[s], ph ^ 1u, a.status, 2);
                 if (!alive) break;
+                trace_event(trace, 2, j, 7);
                 load_kv_tile(a, sq, b, kvh, sm.v[s], &v_map, &sm.v_full[s], j);
             }
             // Make sure none of this CTA's bulk copies is still in flight when it exits: wait
@@ -478,8 +525,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     alive = mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12);
                     if (!alive) break;
                 }
+                trace_event(trace, 2, j, 4);
                 alive = mbar_wait(sm, &sm.v_full[s], ph, a.status, 13);
                 if (!alive) break;
+                trace_event(trace, 2, j, 5);
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
                     // the first 64 keys of P_t arrive while the softmax still works on the other 64:
@@ -538,11 +587,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     for (int i = 0; i < 32; ++i)
                         if (c * 32 + i > limit) sv[c][i] = -INFINITY;
             }
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[c][i]);
+                for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
             trace_event(trace, t, j, 1);
 
@@ -567,26 +617,45 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             }
             const float m_use = (m == -INFINITY) ? 0.0f : m;
-            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // exp2(s * scale - m) two columns at a time: packed FMA for the argument and the row sum;
+            // one pair in four takes its exponential on the FMA pipe (unmasked tiles only), which
+            // relieves the special-function unit the two warpgroups compete for.
+            const unsigned long long scale2 = pack2(a.scale_log2, a.scale_log2);
+            const unsigned long long neg_m2 = pack2(-m_use, -m_use);
+            unsigned long long sum2 = pack2(0.0f, 0.0f);
+            // two straight-line copies (masked tiles keep every exponential on the special-function
+            // unit, where -inf gives an exact zero) rather than a branch inside the unrolled loop
+            auto exp_phase = [&](auto fma_pipe_share) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                unsigned pu[32];
+                for (int c = 0; c < 2; ++c) {
+                    unsigned pu[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int cc = c * 2 + (i >> 4);
-                    const int ii = (i & 15) * 2;
-                    const float p0 = ex2(fmaf(sv[cc][ii], a.scale_log2, -m_use));
-                    const float p1 = ex2(fmaf(sv[cc][ii + 1], a.scale_log2, -m_use));
-                    sum4[i & 3] += p0 + p1;
-                    pu[i] = pack16<T>(p0, p1);
+                    for (int i = 0; i < 32; ++i) {
+                        const int cc = c * 2 + (i >> 4);
+                        const int ii = (i & 15) * 2;
+                        float x0, x1, p0, p1;
+                        unpack2(fma2(pack2(sv[cc][ii], sv[cc][ii + 1]), scale2, neg_m2), x0, x1);
+                        if (decltype(fma_pipe_share)::value && (i & 3) == 3) {
+                            ex2_fma2(x0, x1, p0, p1);
+                        } else {
+                            p0 = ex2(x0);
+                            p1 = ex2(x1);
+                        }
+                        sum2 = add2(sum2, pack2(p0, p1));
+                        pu[i] = pack16<T>(p0, p1);
+                    }
+                    tc_st32(s_addr + c * 32, pu);
+                    tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
+                    if (c == 0) trace_event(trace, t, j, 2);
                 }
-                tc_st32(s_addr + c * 32, pu);
-                tc_wait_st();
-                tc_fence_before();
-                mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
-                if (c == 0) trace_event(trace, t, j, 2);
-            }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            };
+            if (need_mask) exp_phase(std::false_type{});
+            else exp_phase(std::true_type{});
+            float sum_lo, sum_hi;
+            unpack2(sum2, sum_lo, sum_hi);
+            const float sum = sum_lo + sum_hi;
             l = l * alpha + sum;
             trace_event(trace, t, j, 3);
         }
