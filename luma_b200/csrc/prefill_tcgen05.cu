@@ -143,8 +143,9 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
+// Executed by the whole (converged) issuer warp; one elected lane commits.
 __device__ __forceinline__ void tc_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]
@@ -155,6 +156,33 @@ __device__ __forceinline__ void tc_mma_ss(unsigned d_tmem, unsigned long long a_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// The products as the issuer warp runs them: the whole warp executes the instruction stream
+// converged and one elected lane issues. Keeping the warp uniform lets the descriptors live in
+// uniform registers, so a product costs a handful of issue slots; issued from a single diverged
+// lane each needs register-to-uniform moves and, next to ALU-heavy warps on the same scheduler,
+// took ~130 clocks instead of the tensor pipe's 64. The accumulate flag is a compile-time constant.
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ss_imm(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc) {
+    if (kAccumulate)
+        asm volatile("{\n.reg .pred p, e;\nelect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, 1, 0;\n@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n.reg .pred p, e;\nelect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, 0, 0;\n@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void tc_mma_ts_imm(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc) {
+    if (kAccumulate)
+        asm volatile("{\n.reg .pred p, e;\nelect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, 1, 0;\n@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n.reg .pred p, e;\nelect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, 0, 0;\n@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void tc_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc,
@@ -476,35 +504,46 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        {   // the whole warp runs this block converged (see tc_mma_ss_imm)
             const unsigned idesc_qk = make_idesc<T>(false);
             const unsigned idesc_pv = make_idesc<T>(true);
             const TileInfo ts[2] = {t0, t1};
             bool alive = true;
+            // Descriptors are built once; inside the loops an MMA costs one 64-bit add per operand. A
+            // single thread then issues a 128x128x16 product every ~64 clocks, the tensor pipe's own
+            // rate — rebuilding the descriptors per product held it at ~90.
+            const unsigned long long dq[2] = {make_desc(smem_u32(sm.q[0]), 16, 1024), make_desc(smem_u32(sm.q[1]), 16, 1024)};
+            const unsigned long long dk[2] = {make_desc(smem_u32(sm.k[0]), 16, 1024), make_desc(smem_u32(sm.k[1]), 16, 1024)};
+            const unsigned long long dv[2] = {make_desc(smem_u32(sm.v[0]), kHalfBytes, 1024), make_desc(smem_u32(sm.v[1]), kHalfBytes, 1024)};
+            static_assert(kStages == 2, "descriptor tables above hold two stages");
             auto issue_s = [&](int t, int stage) {
                 // S_t = Q_t K^T : 8 K-steps of 16 over d; both operands K-major, 128 B swizzle
-                const unsigned qa = smem_u32(sm.q[t]);
-                const unsigned kb = smem_u32(sm.k[stage]);
+                const unsigned long long qd = t ? dq[1] : dq[0];
+                const unsigned long long kd = stage ? dk[1] : dk[0];
+                const unsigned d_tmem = tmem + t * 128;
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
-                    const unsigned off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-                    tc_mma_ss(tmem + t * 128, make_desc(qa + off, 16, 1024), make_desc(kb + off, 16, 1024), idesc_qk,
-                              kk > 0 ? 1u : 0u);
+                    const unsigned long long inc = (unsigned long long)(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
+                    if (kk == 0) tc_mma_ss_imm<false>(d_tmem, qd + inc, kd + inc, idesc_qk);
+                    else tc_mma_ss_imm<true>(d_tmem, qd + inc, kd + inc, idesc_qk);
                 }
             };
             auto issue_pv = [&](int t, int stage, bool accumulate, int half) {
                 // O_t += P_t V : 8 K-steps of 16 keys; A = P from tensor memory (packed 16-bit, 8 columns
                 // per step), B = V MN-major: 64-column halves 16 KiB apart, 8-key groups 1 KiB apart
-                const unsigned vb = smem_u32(sm.v[stage]);
+                const unsigned long long vd = stage ? dv[1] : dv[0];
+                const unsigned d_tmem = tmem + 256 + t * 128;
+                const unsigned p_tmem = tmem + t * 128;
 #pragma unroll
                 for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
-                    tc_mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, make_desc(vb + kk * 2048, kHalfBytes, 1024),
-                              idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                    const unsigned long long inc = (unsigned long long)((kk * 2048) >> 4);
+                    if (kk == 0 && !accumulate) tc_mma_ts_imm<false>(d_tmem, p_tmem + kk * 8, vd + inc, idesc_pv);
+                    else tc_mma_ts_imm<true>(d_tmem, p_tmem + kk * 8, vd + inc, idesc_pv);
                 }
             };
             for (int t = 0; t < 2 && alive; ++t)
-                if (ts[t].valid) alive = mbar_wait(sm, &sm.q_full[t], 0, a.status, 10);
-            if (alive && n_max > 0) alive = mbar_wait(sm, &sm.k_full[0], 0, a.status, 11);
+                if (ts[t].valid) alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.q_full[t], 0, a.status, 10));
+            if (alive && n_max > 0) alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.k_full[0], 0, a.status, 11));
             trace_event(trace, 2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
             if (alive && n_max > 0) {
                 tc_fence_after();
@@ -522,23 +561,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const int s1 = (j + 1) % kStages;
                 const unsigned ph1 = (unsigned)((j + 1) / kStages) & 1u;
                 if (j + 1 < n_max) {
-                    alive = mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12);
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12));
                     if (!alive) break;
                 }
                 trace_event(trace, 2, j, 4);
-                alive = mbar_wait(sm, &sm.v_full[s], ph, a.status, 13);
+                alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.v_full[s], ph, a.status, 13));
                 if (!alive) break;
                 trace_event(trace, 2, j, 5);
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
                     // the first 64 keys of P_t arrive while the softmax still works on the other 64:
                     // their half of P.V leaves the critical path
-                    alive = mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t);
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t));
                     if (!alive) break;
                     trace_event(trace, 2, j, t * 2);
                     tc_fence_after();
                     issue_pv(t, s, j > 0, 0);
-                    alive = mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t);
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t));
                     if (!alive) break;
                     tc_fence_after();
                     issue_pv(t, s, true, 1);
