@@ -4,7 +4,7 @@
 // batched entry point. Replaces flash_attn_kernel (luma-flash-attn/kernels/flash_attn_func.cu:29-226),
 // a one-thread-per-query-row scalar kernel.
 //
-// One CTA (320 threads, 1 per SM) owns up to two query tiles of 128 rows that share a batch
+// One CTA (384 threads, 1 per SM) owns up to two query tiles of 128 rows that share a batch
 // element and a KV head — two query heads of one GQA group at the same row block, or two
 // consecutive row blocks of one head when the group is 1 — and streams that KV head's K/V tiles
 // (128 keys) past both:
@@ -39,7 +39,7 @@ constexpr int kBlockM = 128;   // query rows per tile
 constexpr int kBlockN = 128;   // keys per K/V tile
 constexpr int kD = 128;        // head size
 constexpr int kStages = 2;     // K ring and V ring depth
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;   // three warpgroups: softmax 0, softmax 1, and producer + issuer (+ two idle warps)
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kTileBytes = kBlockN * kD * 2;        // 32 KiB: two 64-column halves of 128 rows x 128 B
@@ -460,6 +460,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sm.tmem_base;
+    // Register budget: the kernel is compiled for 168 registers per thread (384 threads); the
+    // producer/issuer warpgroup hands most of its share to the two softmax warpgroups, which
+    // keep a whole 128-column score row per thread in registers.
     // only the heaviest CTA of the first (batch, KV head) records its timeline, one thread per role
     long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
     // slot kTraceSteps - 1 of each role holds the CTA's life cycle instead of a kv step
@@ -468,6 +471,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         trace_event(trace, 2, kTraceSteps - 1, 1);   // set-up (barriers, tensor memory) done
     }
 
+    // Register budget: the kernel is compiled for 168 registers per thread (384 threads); the
+    // producer/issuer warpgroup hands most of its share to the two softmax warpgroups, which
+    // keep a whole 128-column score row per thread in registers.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
     if (warp == kLoadWarp) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -590,7 +598,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (j + 1 < n_max) tc_commit(&sm.k_empty[s1]);
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n");
         // ------------------------------ softmax warpgroups ------------------------------
         const int t = warp >> 2;
         const TileInfo ti = t == 0 ? t0 : t1;
