@@ -550,8 +550,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             };
             for (int t = 0; t < 2 && alive; ++t)
-                if (ts[t].valid) alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.q_full[t], 0, a.status, 10));
-            if (alive && n_max > 0) alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.k_full[0], 0, a.status, 11));
+                if (ts[t].valid) alive = (mbar_wait(sm, &sm.q_full[t], 0, a.status, 10));
+            if (alive && n_max > 0) alive = (mbar_wait(sm, &sm.k_full[0], 0, a.status, 11));
             trace_event(trace, 2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
             if (alive && n_max > 0) {
                 tc_fence_after();
@@ -568,24 +568,24 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const unsigned ph = (unsigned)(j / kStages) & 1u;
                 const int s1 = (j + 1) % kStages;
                 const unsigned ph1 = (unsigned)((j + 1) / kStages) & 1u;
-                if (j + 1 < n_max) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12));
-                    if (!alive) break;
-                }
-                trace_event(trace, 2, j, 4);
-                alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.v_full[s], ph, a.status, 13));
+                alive = (mbar_wait(sm, &sm.v_full[s], ph, a.status, 13));
                 if (!alive) break;
-                trace_event(trace, 2, j, 5);
+                bool k_seen = j + 1 >= n_max;   // K(j+1) is first needed for S(j+1): looked at while P's second half is awaited
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
                     // the first 64 keys of P_t arrive while the softmax still works on the other 64:
                     // their half of P.V leaves the critical path
-                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t));
+                    alive = (mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t));
                     if (!alive) break;
                     trace_event(trace, 2, j, t * 2);
                     tc_fence_after();
                     issue_pv(t, s, j > 0, 0);
-                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t));
+                    if (!k_seen) {
+                        alive = (mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12));
+                        if (!alive) break;
+                        k_seen = true;
+                    }
+                    alive = (mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t));
                     if (!alive) break;
                     tc_fence_after();
                     issue_pv(t, s, true, 1);
