@@ -246,7 +246,10 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *   flash_attn_last_launches  : number of kernels that call launched.
  *   flash_attn_set_option     : named integer knobs (returns 0 if the name is known):
  *       "force_generic"       1 = route everything through the SIMT tile kernel
- *       "prefill_trace"       1 = record the timeline read by flash_attn_debug_read
+ *       "prefill_trace"       1 = record the timeline read by flash_attn_debug_read;
+ *                             2 = stage the epilogue's rows in shared memory even for one output;
+ *                             3 = log {start ns, end ns, SM id} of up to 2048 CTAs from byte 16384
+ *       "prefill_trace_y"     blockIdx.y of the CTA whose timeline is recorded (0 = heaviest)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  */
 /*

@@ -61,6 +61,7 @@ struct SharedStorage {
 };
 
 constexpr int kMaxPeers = 8;
+constexpr int kCtaLogEntries = 2048;
 
 struct PrefillArgs {
     // Output: n_out buffers of (batch, q_seq_len, o_heads, 128), each receiving this launch's heads
@@ -73,6 +74,8 @@ struct PrefillArgs {
     float* lse;
     int* status;    // device word, set to non-zero when a bounded wait expired
     long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
+    int trace_y;       // blockIdx.y of the traced CTA (option "prefill_trace_y", default 0 = the heaviest)
+    long long* cta_log;  // optional per-CTA {start ns, end ns, SM id} records ("prefill_trace" = 3), up to kCtaLogEntries
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
     int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
@@ -138,6 +141,13 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
             smem_u32(dst)),
         "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
+}
+
+// Bulk tensor store shared -> global of one box, tracked by the issuing thread's bulk group.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -392,10 +402,11 @@ __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExte
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                       const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+                       const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map, const PrefillArgs a) {
     extern __shared__ unsigned char smem_raw[];
     SharedStorage& sm = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const long long t_entry = clock64();
+    const unsigned long long ns_entry = a.cta_log != nullptr ? global_timer_ns() : 0ULL;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -419,6 +430,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&q_map) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&k_map) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&v_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&o_map) : "memory");
         sm.abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sm.q_full[i], 1);
@@ -464,7 +476,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     // producer/issuer warpgroup hands most of its share to the two softmax warpgroups, which
     // keep a whole 128-column score row per thread in registers.
     // only the heaviest CTA of the first (batch, KV head) records its timeline, one thread per role
-    long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
+    long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == (unsigned)a.trace_y && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
     // slot kTraceSteps - 1 of each role holds the CTA's life cycle instead of a kv step
     if (trace != nullptr && warp == kMmaWarp) {
         trace[(2 * kTraceSteps + kTraceSteps - 1) * 8 + 0] = t_entry;
@@ -717,28 +729,44 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const bool row_ok = row < sq.q_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             if (a.n_out == 1 && !a.staged_store) {
-                // single output: each thread stores its own row straight from registers
-                T* orow = static_cast<T*>(a.o[0]) + ((sq.o_row0 + row) * a.o_heads + a.o_head0 + ti.head) * kD;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    float ov[32];
-                    tc_ld32(o_addr + c * 32, ov);
-                    tc_wait_ld();
-                    if (ti.n_kv == 0) {   // the tile saw no key: tensor memory holds nothing of ours, the rows are zeros
-                    #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = 0.0f;
-                    }
-                    if (row_ok) {
+                // Single output: the rows go out as bulk tensor stores. Each warp lays its 32 rows down in
+                // the Q tile's shared memory (every MMA that read Q_t has finished) in the 128-byte-swizzled
+                // box layout and one lane issues two stores of 32 rows x 64 columns. Plain 16-byte stores
+                // of 32 different rows per instruction would fill the SM's memory pipeline for thousands
+                // of clocks and hold up the barrier traffic of the other tile's last steps. Rows past the
+                // end of the sequence are outside the tensor map and are not written.
+                float ov[4][32];
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 w;
-                            w.x = pack16<T>(ov[i] * inv, ov[i + 1] * inv);
-                            w.y = pack16<T>(ov[i + 2] * inv, ov[i + 3] * inv);
-                            w.z = pack16<T>(ov[i + 4] * inv, ov[i + 5] * inv);
-                            w.w = pack16<T>(ov[i + 6] * inv, ov[i + 7] * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
-                        }
+                for (int c = 0; c < 4; ++c) tc_ld32(o_addr + c * 32, ov[c]);
+                tc_wait_ld();
+                if (ti.n_kv == 0) {   // the tile saw no key: tensor memory holds nothing of ours, the rows are zeros
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[c][i] = 0.0f;
+                }
+                unsigned char* stage = sm.q[t];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack16<T>(ov[c][8 * i] * inv, ov[c][8 * i + 1] * inv);
+                        w.y = pack16<T>(ov[c][8 * i + 2] * inv, ov[c][8 * i + 3] * inv);
+                        w.z = pack16<T>(ov[c][8 * i + 4] * inv, ov[c][8 * i + 5] * inv);
+                        w.w = pack16<T>(ov[c][8 * i + 6] * inv, ov[c][8 * i + 7] * inv);
+                        const int ch = (c & 1) * 4 + i;   // 16-byte chunk within the 64-column half c >> 1
+                        *reinterpret_cast<uint4*>(stage + (c >> 1) * kHalfBytes + r * 128 + ((ch ^ (r & 7)) << 4)) = w;
                     }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> bulk copy reads
+                __syncwarp();
+                if (lane == 0) {
+                    const int warp_row0 = (warp & 3) * 32;
+                    tma_store_4d(&o_map, stage + warp_row0 * 128, 0, a.o_head0 + ti.head, sq.q_crow + ti.row0 + warp_row0, sq.q_cb);
+                    tma_store_4d(&o_map, stage + kHalfBytes + warp_row0 * 128, 64, a.o_head0 + ti.head, sq.q_crow + ti.row0 + warp_row0, sq.q_cb);
+                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // shared memory stays valid until read
                 }
             } else {
                 // Stage this warp's 32 rows (256 B each) in the Q tile's shared memory — every MMA that read
@@ -798,6 +826,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
     }
+    if (a.cta_log != nullptr && threadIdx.x == 0) {
+        const int idx = blockIdx.y * gridDim.x + blockIdx.x;
+        if (idx < kCtaLogEntries) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;\n" : "=r"(smid));
+            a.cta_log[idx * 3 + 0] = (long long)ns_entry;
+            a.cta_log[idx * 3 + 1] = (long long)global_timer_ns();
+            a.cta_log[idx * 3 + 2] = (long long)smid;
+        }
+    }
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -822,12 +860,12 @@ EncodeFn get_encode_fn() {
 }
 
 // (batch, seq, heads, 128) 16-bit tensor viewed as 4-D {d, head, seq, batch}; box = 64 x 1 x 128 x 1
-bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads) {
+bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int box_rows = kBlockM) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
     const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2, (cuuint64_t)seq * heads * kD * 2};
-    const cuuint32_t box[4] = {64, 1, (cuuint32_t)kBlockM, 1};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUresult rc = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -854,7 +892,7 @@ bool encode_paged_map(CUtensorMap* map, const void* base, int dtype, int block_s
 }
 
 // Per-device debug area: the status word, then (from byte 256) the optional timeline.
-constexpr size_t kDebugBytes = 65536;
+constexpr size_t kDebugBytes = 16384 + kCtaLogEntries * 24;
 std::mutex g_status_mutex;
 int* g_status_word[64] = {nullptr};
 
@@ -876,8 +914,11 @@ int* status_word() {
 
 template <typename T>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
-    CUtensorMap qm, km, vm;
+    CUtensorMap qm, km, vm, om;
     bool ok = encode_map(&qm, p.q, p.dtype, p.num_seqs, p.q_seq_len, p.q_heads);
+    // the output as 32-row boxes (one per softmax warp); only used when there is a single output buffer
+    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, p.num_seqs, p.q_seq_len,
+                          p.n_out > 0 ? p.o_heads : p.q_heads, 32);
     if (p.paged) {
         ok = ok && encode_paged_map(&km, p.k, p.dtype, p.block_size, p.kv_heads) &&
              encode_paged_map(&vm, p.v, p.dtype, p.block_size, p.kv_heads);
@@ -905,6 +946,8 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.lse = p.lse;
     a.status = status;
     a.staged_store = get_option_prefill_trace() == 2 ? 1 : 0;
+    a.trace_y = get_option_prefill_trace_y();
+    a.cta_log = get_option_prefill_trace() == 3 ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 16384) : nullptr;
     a.trace = get_option_prefill_trace() == 1 ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
     a.batch = p.num_seqs;
     a.q_seq_len = p.q_seq_len;
@@ -933,7 +976,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         return FLASH_ATTN_ERR_CUDA;
     }
     dim3 grid(p.kv_heads * p.num_seqs, pairs);
-    prefill_tcgen05_kernel<T><<<grid, kThreads, smem, stream>>>(qm, km, vm, a);
+    prefill_tcgen05_kernel<T><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
     const int rc = check_launch("prefill_tcgen05_kernel");
     if (rc == FLASH_ATTN_OK) note_path("prefill_tcgen05", 1);
     return rc;
