@@ -102,6 +102,27 @@ int flash_attn_varlen_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* 
                            void* stream);
 
 /*
+ * ADDITIVE (no counterpart in the reference): the packed entry point with the row counts of the
+ * packed buffers, which lets f16/bf16 head_size-128 calls run on the tensor-core kernel (its bulk
+ * copies need the buffers' extents; the reference signature above only has them on the device, in
+ * cu_seqlens[num_seqs]). luma's high.rs knows both from the tensor shapes (high.rs:170-182).
+ *   total_q : rows of q and o (= cu_seqlens_q[num_seqs])
+ *   total_k : rows of contiguous k and v (= cu_seqlens_k[num_seqs]); ignored when k_paged != 0
+ * Same checks, results and status codes as flash_attn_varlen_{f16,bf16}; totals <= 0 mean
+ * "unknown" and give exactly the behaviour of those.
+ */
+int flash_attn_varlen_f16_total(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                flash_attn_f16_t* o, const int* cu_seqlens_q, const int* cu_seqlens_k,
+                                const int* block_tables, int num_seqs, int max_seqlen_q, int max_seqlen_k,
+                                int q_heads, int kv_heads, int head_size, int block_size, int max_blocks,
+                                int k_paged, float scale, int total_q, int total_k, void* stream);
+int flash_attn_varlen_bf16_total(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                 flash_attn_bf16_t* o, const int* cu_seqlens_q, const int* cu_seqlens_k,
+                                 const int* block_tables, int num_seqs, int max_seqlen_q, int max_seqlen_k,
+                                 int q_heads, int kv_heads, int head_size, int block_size, int max_blocks,
+                                 int k_paged, float scale, int total_q, int total_k, void* stream);
+
+/*
  * Attention over a paged KV cache: q_seq_len == 1 is single-token decode, > 1 is chunked
  * prefill (bottom-right causal: row i sits at context_lens[s] - q_seq_len + i).
  * Replaces flash_attn_with_kvcache_{f32,f16,bf16} (ffi.rs:134-189;

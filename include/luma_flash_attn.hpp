@@ -92,12 +92,14 @@ template <> struct FlashDtype<f16> {
     using raw = flash_attn_f16_t;
     static constexpr auto batch = &flash_attn_f16;
     static constexpr auto varlen = &flash_attn_varlen_f16;
+    static constexpr auto varlen_total = &flash_attn_varlen_f16_total;
     static constexpr auto kvcache = &flash_attn_with_kvcache_f16;
 };
 template <> struct FlashDtype<bf16> {
     using raw = flash_attn_bf16_t;
     static constexpr auto batch = &flash_attn_bf16;
     static constexpr auto varlen = &flash_attn_varlen_bf16;
+    static constexpr auto varlen_total = &flash_attn_varlen_bf16_total;
     static constexpr auto kvcache = &flash_attn_with_kvcache_bf16;
 };
 
@@ -180,6 +182,36 @@ void flash_attn_varlen(const DeviceSlice<const T>& q, const DeviceSlice<const T>
         reinterpret_cast<const R*>(q.ptr), reinterpret_cast<const R*>(k.ptr), reinterpret_cast<const R*>(v.ptr),
         reinterpret_cast<R*>(o.ptr), cu_seqlens_q.ptr, cu_seqlens_k.ptr, block_tables ? block_tables->ptr : nullptr, num_seqs,
         max_seqlen_q, max_seqlen_k, q_heads, kv_heads, head_size, block_size, max_blocks, k_paged, scale, stream);
+    FlashAttnError::from_status(code);
+}
+
+// Additive (16-bit storage only): the same call with the row counts of the packed buffers, which the
+// caller knows from its tensor shapes (high.rs:170-182) and a slice length does not tell (a slice
+// may be longer than the packed data). With them head_size-128 calls run on the tensor-core kernel.
+template <typename T>
+void flash_attn_varlen_total(const DeviceSlice<const T>& q, const DeviceSlice<const T>& k, const DeviceSlice<const T>& v,
+                             DeviceSlice<T>& o, const DeviceSlice<const int>& cu_seqlens_q,
+                             const DeviceSlice<const int>& cu_seqlens_k, int num_seqs, int max_seqlen_q, int max_seqlen_k,
+                             int q_heads, int kv_heads, int head_size, float scale, const DeviceSlice<const int>* block_tables,
+                             int block_size, int total_q, int total_k, void* stream) {
+    using R = typename FlashDtype<T>::raw;
+    if (total_q > 0 && q_heads > 0 && head_size > 0) {
+        const uint64_t q_need = static_cast<uint64_t>(total_q) * q_heads * head_size;
+        check_len("q", q.len, q_need);
+        check_len("o", o.len, q_need);
+    }
+    if (total_k > 0 && block_tables == nullptr && kv_heads > 0 && head_size > 0) {
+        const uint64_t kv_need = static_cast<uint64_t>(total_k) * kv_heads * head_size;
+        check_len("k", k.len, kv_need);
+        check_len("v", v.len, kv_need);
+    }
+    const int k_paged = block_tables != nullptr ? 1 : 0;
+    const int max_blocks = (block_tables != nullptr && num_seqs > 0) ? static_cast<int>(block_tables->len / num_seqs) : 0;
+    const int code = FlashDtype<T>::varlen_total(
+        reinterpret_cast<const R*>(q.ptr), reinterpret_cast<const R*>(k.ptr), reinterpret_cast<const R*>(v.ptr),
+        reinterpret_cast<R*>(o.ptr), cu_seqlens_q.ptr, cu_seqlens_k.ptr, block_tables ? block_tables->ptr : nullptr, num_seqs,
+        max_seqlen_q, max_seqlen_k, q_heads, kv_heads, head_size, block_size, max_blocks, k_paged, scale, total_q, total_k,
+        stream);
     FlashAttnError::from_status(code);
 }
 

@@ -192,7 +192,8 @@ int batch_impl(int dtype, const void* q, const void* k, const void* v, void* o, 
 int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
                 const int* cu_seqlens_q, const int* cu_seqlens_k, const int* block_tables,
                 int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads, int kv_heads,
-                int head_size, int block_size, int max_blocks, int k_paged, float scale, void* stream) {
+                int head_size, int block_size, int max_blocks, int k_paged, float scale, void* stream,
+                int total_q = 0, int total_k = 0) {
     g_last_error[0] = '\0';
     cudaGetLastError();
     if (q == nullptr || o == nullptr || cu_seqlens_q == nullptr || cu_seqlens_k == nullptr) {
@@ -235,6 +236,8 @@ int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
     p.block_size = block_size;
     p.max_blocks = max_blocks;
     p.paged = k_paged ? 1 : 0;
+    p.total_q = total_q > 0 ? total_q : 0;
+    p.total_k = total_k > 0 ? total_k : 0;
     p.scale = scale;
     return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
 }
@@ -438,6 +441,25 @@ FA_DEFINE_VARLEN(flash_attn_varlen_f32, float, fa::DT_F32)
 FA_DEFINE_VARLEN(flash_attn_varlen_f16, flash_attn_f16_t, fa::DT_F16)
 FA_DEFINE_VARLEN(flash_attn_varlen_bf16, flash_attn_bf16_t, fa::DT_BF16)
 #undef FA_DEFINE_VARLEN
+
+int flash_attn_varlen_f16_total(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                flash_attn_f16_t* o, const int* cu_seqlens_q, const int* cu_seqlens_k,
+                                const int* block_tables, int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads,
+                                int kv_heads, int head_size, int block_size, int max_blocks, int k_paged, float scale,
+                                int total_q, int total_k, void* stream) {
+    return fa::varlen_impl(fa::DT_F16, q, k, v, o, cu_seqlens_q, cu_seqlens_k, block_tables, num_seqs, max_seqlen_q,
+                           max_seqlen_k, q_heads, kv_heads, head_size, block_size, max_blocks, k_paged, scale, stream,
+                           total_q, total_k);
+}
+int flash_attn_varlen_bf16_total(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                 flash_attn_bf16_t* o, const int* cu_seqlens_q, const int* cu_seqlens_k,
+                                 const int* block_tables, int num_seqs, int max_seqlen_q, int max_seqlen_k, int q_heads,
+                                 int kv_heads, int head_size, int block_size, int max_blocks, int k_paged, float scale,
+                                 int total_q, int total_k, void* stream) {
+    return fa::varlen_impl(fa::DT_BF16, q, k, v, o, cu_seqlens_q, cu_seqlens_k, block_tables, num_seqs, max_seqlen_q,
+                           max_seqlen_k, q_heads, kv_heads, head_size, block_size, max_blocks, k_paged, scale, stream,
+                           total_q, total_k);
+}
 
 #define FA_DEFINE_KVCACHE(NAME, CTYPE, DT)                                                          \
     int NAME(const CTYPE* q, const CTYPE* k_cache, const CTYPE* v_cache, CTYPE* o,                  \

@@ -45,6 +45,10 @@ struct AttnParams {
     int block_size;
     int max_blocks;
     int paged;
+    // MODE_VARLEN only: rows of the packed q/o and of the packed (contiguous) k/v buffers, when the
+    // caller can say (0 = unknown: the tensor-core path needs them to bound its bulk copies)
+    int total_q;
+    int total_k;
     float scale;
     // head-sharded output (tcgen05 prefill only): n_out > 0 replaces `o` by n_out buffers of
     // (batch, q_seq_len, o_heads, head_size) that each receive this call's heads at o_head0

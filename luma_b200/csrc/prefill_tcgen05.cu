@@ -728,7 +728,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_after();
             const bool row_ok = row < sq.q_len;
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            if (a.n_out == 1 && !a.staged_store) {
+            // a bulk store writes every row of its box that lies inside the tensor: in a packed buffer the
+            // rows after this sequence belong to the next one, so a tile that overhangs the end of its
+            // sequence takes the row-guarded path
+            const bool bulk_ok = a.n_out == 1 && !a.staged_store && (a.mode != MODE_VARLEN || ti.row0 + kBlockM <= sq.q_len);
+            if (bulk_ok) {
                 // Single output: the rows go out as bulk tensor stores. Each warp lays its 32 rows down in
                 // the Q tile's shared memory (every MMA that read Q_t has finished) in the 128-byte-swizzled
                 // box layout and one lane issues two stores of 32 rows x 64 columns. Plain 16-byte stores
@@ -915,16 +919,20 @@ int* status_word() {
 template <typename T>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
     CUtensorMap qm, km, vm, om;
-    bool ok = encode_map(&qm, p.q, p.dtype, p.num_seqs, p.q_seq_len, p.q_heads);
+    // packed varlen buffers are one "batch" of total rows
+    const bool packed = p.mode == MODE_VARLEN;
+    const int q_batch = packed ? 1 : p.num_seqs, q_rows = packed ? p.total_q : p.q_seq_len;
+    const int k_batch = packed ? 1 : p.num_seqs, k_rows = packed ? p.total_k : p.kv_seq_len;
+    bool ok = encode_map(&qm, p.q, p.dtype, q_batch, q_rows, p.q_heads);
     // the output as 32-row boxes (one per softmax warp); only used when there is a single output buffer
-    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, p.num_seqs, p.q_seq_len,
+    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, q_batch, q_rows,
                           p.n_out > 0 ? p.o_heads : p.q_heads, 32);
     if (p.paged) {
         ok = ok && encode_paged_map(&km, p.k, p.dtype, p.block_size, p.kv_heads) &&
              encode_paged_map(&vm, p.v, p.dtype, p.block_size, p.kv_heads);
     } else {
-        ok = ok && encode_map(&km, p.k, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads) &&
-             encode_map(&vm, p.v, p.dtype, p.num_seqs, p.kv_seq_len, p.kv_heads);
+        ok = ok && encode_map(&km, p.k, p.dtype, k_batch, k_rows, p.kv_heads) &&
+             encode_map(&vm, p.v, p.dtype, k_batch, k_rows, p.kv_heads);
     }
     if (!ok) return -1;  // let the SIMT kernel take it
     int* status = status_word();
@@ -1008,16 +1016,20 @@ int prefill_debug_read(void* dst, int bytes) {
 }
 
 int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
-    // batched entry point, and chunked prefill over a paged cache (whole pages must tile the 128-key
-    // K/V tile). The packed varlen entry point stays on the SIMT kernel: its C ABI carries no total
-    // row counts, so a tensor map with exact bounds cannot be built on the host.
+    // batched entry point, chunked prefill over a paged cache (whole pages must tile the 128-key
+    // K/V tile), and the packed varlen entry point when the caller said how many rows the packed
+    // buffers have (the reference signature does not: without them no tensor map with exact bounds
+    // can be built on the host, and the call stays on the SIMT kernel).
     if (p.mask != nullptr) return -1;
     if (p.mode == MODE_KVCACHE) {
         if (!p.paged || p.max_blocks <= 0) return -1;
-        if (p.block_size < 8 || p.block_size > 128 || (128 % p.block_size) != 0) return -1;
+    } else if (p.mode == MODE_VARLEN) {
+        if (p.total_q <= 0) return -1;
+        if (p.paged ? p.max_blocks <= 0 : p.total_k <= 0) return -1;
     } else if (p.mode != MODE_BATCH) {
         return -1;
     }
+    if (p.paged && (p.block_size < 8 || p.block_size > 128 || (128 % p.block_size) != 0)) return -1;
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
     if (p.head_size != kD) return -1;
     if (!(p.scale > 0.0f)) return -1;

@@ -38,10 +38,15 @@ EXPORTED_SYMBOLS = (
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
     + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather",
-       "flash_attn_kvcache_append"]
+       "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total"]
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
+
+_VARLEN_TOTAL_ARGS = _VARLEN_ARGS[:-1] + [c_int, c_int, c_void_p]
+for _s in ("f16", "bf16"):
+    getattr(lib, f"flash_attn_varlen_{_s}_total").argtypes = _VARLEN_TOTAL_ARGS
+    getattr(lib, f"flash_attn_varlen_{_s}_total").restype = c_int
 
 for _s in DTYPE_SUFFIX:
     getattr(lib, f"flash_attn_{_s}").argtypes = _BATCH_ARGS

@@ -109,3 +109,104 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens, block_table,
     low.flash_attn_with_kvcache(q, k_cache, v_cache, o, block_table.contiguous(), cache_seqlens.contiguous(),
                                 b, sq, hq, hkv, d, block_size, max_blocks, scale)
     return o
+
+
+class _HostPipe:
+    """Streams, events and device staging buffers of `flash_attn_func_host`, kept per device."""
+
+    def __init__(self, device):
+        self.device = device
+        self.s_in = torch.cuda.Stream(device)
+        self.s_run = torch.cuda.Stream(device)
+        self.s_out = torch.cuda.Stream(device)
+        self.key = None
+        self.slots = []
+
+    def buffers(self, key, make):
+        if self.key != key:
+            self.slots = [make() for _ in range(2)]
+            self.key = key
+        return self.slots
+
+
+_host_pipes = {}
+
+
+def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = None, causal: bool = True,
+                         start_pos: int = 0, device=None):
+    """Batched attention for HOST tensors (this library's addition; luma has no counterpart).
+
+    q (B, Sq, Hq, d), k, v (B, Skv, Hkv, d) in (preferably pinned) host memory -> `out` (B, Sq, Hq, d)
+    in host memory (allocated pinned when None). The batch elements are independent, so they are
+    pipelined one at a time over three streams: while element i is in the kernel, element i+1 is
+    on its way to the device and the result of element i-1 on its way back, which keeps both
+    directions of the host link busy instead of using them in turn. The caller's current stream
+    waits for the last copy; `out` is complete when that stream has caught up.
+    """
+    if not causal:
+        raise E.Unsupported("flash_attn_func_host: non-causal is not supported yet (kernels are causal-only)")
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise E.Unsupported("flash_attn_func_host: q/k/v must be host tensors (use flash_attn_func for device tensors)")
+    if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise E.Unsupported(f"flash_attn_func_host: dtype {q.dtype} (only f32/f16/bf16)")
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise E.InvalidShape("flash_attn_func_host: q/k/v must be rank 4")
+    b, sq, hq, d = q.shape
+    bk, skv, hkv, dk = k.shape
+    if tuple(v.shape) != tuple(k.shape) or bk != b or dk != d:
+        raise E.InvalidShape(f"flash_attn_func_host: incompatible shapes q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise E.Unsupported("flash_attn_func_host: q/k/v dtypes differ")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(d)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    elif out.is_cuda or tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+        raise E.InvalidShape("flash_attn_func_host: out must be a contiguous host tensor shaped and typed like q")
+
+    pipe = _host_pipes.get(dev)
+    if pipe is None:
+        pipe = _host_pipes[dev] = _HostPipe(dev)
+    key = (sq, skv, hq, hkv, d, q.dtype)
+
+    def make():
+        return {"q": torch.empty((1, sq, hq, d), dtype=q.dtype, device=dev),
+                "k": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
+                "v": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
+                "o": torch.empty((1, sq, hq, d), dtype=q.dtype, device=dev),
+                "ran": None, "out": None}
+
+    slots = pipe.buffers(key, make)
+    cur = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(cur)
+    pipe.s_in.wait_event(start)
+    last = None
+    for i in range(b):
+        sl = slots[i & 1]
+        # the slot's inputs are free once its previous kernel has run, its output once copied back
+        if sl["ran"] is not None:
+            pipe.s_in.wait_event(sl["ran"])
+        with torch.cuda.stream(pipe.s_in):
+            sl["q"].copy_(q[i:i + 1], non_blocking=True)
+            sl["k"].copy_(k[i:i + 1], non_blocking=True)
+            sl["v"].copy_(v[i:i + 1], non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(pipe.s_in)
+        pipe.s_run.wait_event(arrived)
+        if sl["out"] is not None:
+            pipe.s_run.wait_event(sl["out"])
+        low.flash_attn(sl["q"], sl["k"], sl["v"], sl["o"], 1, sq, skv, hq, hkv, d, int(start_pos), scale, None,
+                       pipe.s_run, None)
+        sl["ran"] = torch.cuda.Event()
+        sl["ran"].record(pipe.s_run)
+        pipe.s_out.wait_event(sl["ran"])
+        with torch.cuda.stream(pipe.s_out):
+            out[i:i + 1].copy_(sl["o"], non_blocking=True)
+            sl["out"] = torch.cuda.Event()
+            sl["out"].record(pipe.s_out)
+        last = sl["out"]
+    if last is not None:
+        cur.wait_event(last)
+    return out

@@ -131,3 +131,23 @@ def test_offset_views_are_bit_identical():
             return flat[pad:].view(*x.shape)
         viewed = high.flash_attn_func(shifted(q), shifted(k), shifted(v))
         assert torch.equal(direct, viewed)
+
+
+def test_host_tensor_call_matches_device_call():
+    """flash_attn_func_host (pinned host tensors, batch elements pipelined over three streams) gives
+    the same bits as the device call, twice in a row (staging buffers and events are reused)."""
+    torch.manual_seed(7)
+    b, s, hq, hkv, d = 3, 300, 4, 2, 128
+    q = torch.randn(b, s, hq, d).bfloat16().pin_memory()
+    k = torch.randn(b, s, hkv, d).bfloat16().pin_memory()
+    v = torch.randn(b, s, hkv, d).bfloat16().pin_memory()
+    want = high.flash_attn_func(q.cuda(), k.cuda(), v.cuda()).cpu()
+    out = torch.empty_like(q).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        got = high.flash_attn_func_host(q, k, v, out)
+        torch.cuda.current_stream().synchronize()
+        assert got is out
+        assert torch.equal(out, want)
+    with pytest.raises(L.Unsupported):
+        high.flash_attn_func_host(q.cuda(), k, v)
