@@ -269,6 +269,44 @@ def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, l
     }
 
 
+def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d, steps, warmup, peaks, seed):
+    """Packed variable-length prefill (the serving shape of the batched config): `num_seqs` prompts of
+    lo..hi tokens packed back to back, square causal per prompt, through flash_attn_varlen_bf16_total."""
+    rng = np.random.Generator(np.random.Philox(seed))
+    lens = rng.integers(lo, hi + 1, size=num_seqs).astype(np.int64)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed + 1)
+    q = torch.randn(total, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(total, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn(total, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    cu_d = torch.from_numpy(cu).to(dev)
+    scale = 1.0 / math.sqrt(d)
+    max_len = int(lens.max())
+
+    def step():
+        low.flash_attn_varlen(q, k, v, o, cu_d, cu_d, num_seqs, max_len, max_len, hq, hkv, d, scale,
+                              total_q=total, total_k=total)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches()
+    sec = time_steps(torch, step, steps, warmup)
+    flops = sum(causal_flops(1, hq, int(L), int(L), d) for L in lens)
+    tf = flops * steps / sec / 1e12
+    peak = peaks["bf16_tflops"]
+    return {
+        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+        "kernel_path": path, "launches_per_step": launches,
+        "config": {"workload": name, "num_seqs": num_seqs, "prompt_tokens": [int(lo), int(hi)], "total_tokens": total,
+                   "q_heads": hq, "kv_heads": hkv, "head_dim": d, "flops_per_step": flops,
+                   "l2_policy": "inputs larger than L2"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)", "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
+    }
+
+
 NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool (nominal 900)
 
 
@@ -499,6 +537,8 @@ def main():
         elif name == "prefill_c3_small":   # one batch element, 8 of 32 heads: same kernel, short capture
             res, _ = run_prefill(torch, low, ffi, dev, name, 1, 8, 2, 8192, 128, args.steps, args.warmup, peaks, seed=3,
                                  scale_in=0.5, want_lse=False)
+        elif name == "varlen_prefill":
+            res = run_varlen_prefill(torch, low, ffi, dev, name, 32, 1024, 8192, 32, 8, 128, args.steps, args.warmup, peaks, seed=7)
         elif name == "decode_c4":
             res, _ = run_decode(torch, low, ffi, dev, name, 64, 32, 8, 128, 16, 512, 8192, 40000, args.steps, args.warmup,
                                 peaks, seed=4)
@@ -601,6 +641,11 @@ def main():
             # the step before decode (not a BASELINE config): 1024-token chunks over paged contexts
             workloads["paged_prefill"] = run_paged_prefill(torch, low, ffi, dev, "paged_prefill", 16, 1024, 32, 8, 128, 16,
                                                            1024, 8192, extra_steps, 3, peaks, seed=6)
+            torch.cuda.empty_cache()
+        if only in (None, "varlen_prefill"):
+            # not a BASELINE config: 32 prompts of 1024..8192 tokens packed, GQA 32/8 (q+k+v+o = 230 MB at the mean)
+            workloads["varlen_prefill"] = run_varlen_prefill(torch, low, ffi, dev, "varlen_prefill", 32, 1024, 8192, 32, 8, 128,
+                                                             extra_steps, 3, peaks, seed=7)
             torch.cuda.empty_cache()
         if only in (None, "decode_c4"):
             workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,
