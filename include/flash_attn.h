@@ -271,6 +271,7 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *                             2 = stage the epilogue's rows in shared memory even for one output;
  *                             3 = log {start ns, end ns, SM id} of up to 2048 CTAs from byte 16384
  *       "prefill_trace_y"     blockIdx.y of the CTA whose timeline is recorded (0 = heaviest)
+ *       "prefill_band"        tile pairs of one K/V stream launched next to each other (0 = automatic)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  */
 /*

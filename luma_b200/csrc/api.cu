@@ -23,6 +23,7 @@ int g_force_generic = 0;
 int g_decode_chunk = 0;
 int g_prefill_trace = 0;
 int g_prefill_trace_y = 0;
+int g_prefill_band = 0;
 }  // namespace
 
 void set_last_error(const char* msg) { std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
@@ -43,6 +44,7 @@ int get_option_force_generic() { return g_force_generic; }
 int get_option_decode_chunk() { return g_decode_chunk; }
 int get_option_prefill_trace() { return g_prefill_trace; }
 int get_option_prefill_trace_y() { return g_prefill_trace_y; }
+int get_option_prefill_band() { return g_prefill_band; }
 
 int check_launch(const char* what) {
     const cudaError_t err = cudaGetLastError();
@@ -395,6 +397,10 @@ int flash_attn_set_option(const char* name, int value) {
     }
     if (std::strcmp(name, "prefill_trace") == 0) {
         fa::g_prefill_trace = value;
+        return 0;
+    }
+    if (std::strcmp(name, "prefill_band") == 0) {
+        fa::g_prefill_band = value;
         return 0;
     }
     if (std::strcmp(name, "prefill_trace_y") == 0) {

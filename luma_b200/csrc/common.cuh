@@ -124,6 +124,7 @@ int get_option_force_generic();
 int get_option_decode_chunk();
 int get_option_prefill_trace();
 int get_option_prefill_trace_y();
+int get_option_prefill_band();
 
 // Returns FLASH_ATTN_OK or FLASH_ATTN_ERR_CUDA (with last error set) after a launch.
 int check_launch(const char* what);

@@ -26,6 +26,7 @@
 // tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -77,6 +78,7 @@ struct PrefillArgs {
     int trace_y;       // blockIdx.y of the traced CTA (option "prefill_trace_y", default 0 = the heaviest)
     long long* cta_log;  // optional per-CTA {start ns, end ns, SM id} records ("prefill_trace" = 3), up to kCtaLogEntries
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
+    int band;       // tile pairs of one (batch, KV head) that sit next to each other in blockIdx.x
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
     int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
     const int* cu_q;            // MODE_VARLEN: packed row offsets of q / o
@@ -411,11 +413,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int group = a.q_heads / a.kv_heads;
-    const SeqExtent sq = seq_extent(a, blockIdx.x / a.kv_heads);
+    // blockIdx.x = (batch element, KV head) x `band` neighbouring tile pairs, blockIdx.y = band of pairs,
+    // heaviest (latest rows) first. CTAs are dispatched in index order, so the `band` CTAs that walk
+    // the same K/V stream start together and meet its tiles in L2 instead of each pulling them from
+    // HBM, while the order across bands stays heaviest first.
+    const int stream_id = blockIdx.x / a.band;
+    const SeqExtent sq = seq_extent(a, stream_id / a.kv_heads);
     const int num_mb = (sq.q_len + kBlockM - 1) / kBlockM;
-    const int kvh = blockIdx.x % a.kv_heads;
-    const int b = blockIdx.x / a.kv_heads;
-    const int pair = gridDim.y - 1 - blockIdx.y;   // heaviest (latest rows) first
+    const int kvh = stream_id % a.kv_heads;
+    const int b = stream_id / a.kv_heads;
+    const int pair = (gridDim.y - 1 - blockIdx.y) * a.band + (a.band - 1 - (int)(blockIdx.x % a.band));
 
     const TileInfo t0 = tile_info(sq, pair, 0, kvh, group, num_mb);
     const TileInfo t1 = tile_info(sq, pair, 1, kvh, group, num_mb);
@@ -983,7 +990,11 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         cudaGetLastError();
         return FLASH_ATTN_ERR_CUDA;
     }
-    dim3 grid(p.kv_heads * p.num_seqs, pairs);
+    // up to 8 neighbouring pairs per band, but at least 16 bands so that the order stays heaviest first
+    const int band = get_option_prefill_band() > 0 ? std::min(get_option_prefill_band(), pairs) : std::max(1, std::min(8, pairs / 16));
+    a.band = band;
+    if ((long long)p.kv_heads * p.num_seqs * band > 0x7fffffffLL) return -1;
+    dim3 grid(p.kv_heads * p.num_seqs * band, (pairs + band - 1) / band);
     prefill_tcgen05_kernel<T><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
     const int rc = check_launch("prefill_tcgen05_kernel");
     if (rc == FLASH_ATTN_OK) note_path("prefill_tcgen05", 1);
