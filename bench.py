@@ -81,15 +81,31 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
+                 "-lms", "50", "-i", str(self.gpu_index)],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, torch=None, step=None, barrier=None, repeats=None):
+        """Ends the sampling and summarises it. The timed region of a step is a few milliseconds,
+        shorter than nvidia-smi's start-up: when `step` is given, the same step is first repeated,
+        untimed, for about 0.35 s so that there are samples under this very load."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
+        if step is not None and torch is not None:
+            # with several ranks the caller passes `repeats` (every rank must make the same number of
+            # collective calls); alone the count comes from one timed call
+            if repeats is None:
+                t0 = time.time()
+                step()
+                torch.cuda.synchronize()
+                repeats = int(0.35 / max(time.time() - t0, 1e-5))
+            for _ in range(max(1, min(20000, int(repeats)))):
+                step()
+            torch.cuda.synchronize()
+            if barrier is not None:
+                barrier()
         time.sleep(0.15)
         self.proc.terminate()
         try:
@@ -116,6 +132,8 @@ class ClockSampler:
         if sm:
             out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
                    "samples": len(sm)}
+            if step is not None:
+                out["note"] = "sampled from the start of the timed region through an untimed ~0.35 s repeat of the same step"
         return out
 
 
@@ -563,8 +581,8 @@ def main():
     if world == 1:
         sampler.start()
         primary, bufs = run_prefill(torch, low, ffi, dev, "prefill_c2", b, hq, hkv, s, d, K, W, peaks, seed=2)
-        clocks = sampler.stop()
         q, k, v, o, lse = bufs
+        clocks = sampler.stop(torch, lambda: low.flash_attn(q, k, v, o, b, s, s, hq, hkv, d, 0, 1.0 / math.sqrt(d), None, None, lse))
         scaling_note = "single GPU"
     else:
         from luma_b200 import dist as fdist
@@ -583,10 +601,10 @@ def main():
         path, launches = ffi.last_path(), ffi.last_launches() + 1
         sampler.start()
         sec = time_steps(torch, step, K, W, barrier)
-        clocks = sampler.stop()
         t = torch.tensor([sec], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec = float(t.item())
+        clocks = sampler.stop(torch, step, barrier, repeats=0.35 / max(sec / K, 1e-6))
         flops = causal_flops(b, hq, s, s, d) * world
         tf = flops * K / sec / 1e12
         primary = {
