@@ -13,7 +13,7 @@
 //                     the scale folded in), write P as packed 16-bit back over S (tcgen05.st),
 //                     rescale O in tensor memory only when the row max moved by more than 2^8,
 //                     final normalisation and store of O (and LSE)
-//   warp 8          : TMA producer — Q once, then K and V tiles through two 2-stage rings
+//   warp 8 / 10     : TMA producers — warp 8 loads Q once, then the K tiles; warp 10 the V tiles; two 2-stage rings
 //   warp 9          : MMA issuer — S_t = Q_t K^T (SS form), O_t += P_t V (P from tensor memory),
 //                     completion signalled with tcgen05.commit on mbarriers
 // While one warpgroup runs its softmax the tensor core works on the other tile.
@@ -43,6 +43,7 @@ constexpr int kStages = 2;     // K ring and V ring depth
 constexpr int kThreads = 384;   // three warpgroups: softmax 0, softmax 1, and producer + issuer (+ two idle warps)
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
+constexpr int kLoadWarpV = 10;   // V-ring producer (K ring and Q: kLoadWarp)
 constexpr int kTileBytes = kBlockN * kD * 2;        // 32 KiB: two 64-column halves of 128 rows x 128 B
 constexpr int kHalfBytes = kTileBytes / 2;
 constexpr float kRescaleThreshold = 8.0f;            // log2 units
@@ -465,11 +466,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         load_q(t0, 0);
         if (n_pre > 0) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
         load_q(t1, 1);
-        if (n_pre > 0) load_kv(sm.v[0], &v_map, &sm.v_full[0], 0);
-        for (int j = 1; j < n_pre; ++j) {
-            load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
-            load_kv(sm.v[j], &v_map, &sm.v_full[j], j);
-        }
+        for (int j = 1; j < n_pre; ++j) load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
+        // the V tiles come from a producer thread of their own (warp kLoadWarpV), after the set-up barrier
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(smem_u32(&sm.tmem_base)) : "memory");
@@ -495,38 +493,40 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     // keep a whole 128-column score row per thread in registers.
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
-    if (warp == kLoadWarp) {
-        // ------------------------------ TMA producer ------------------------------
+    if (warp == kLoadWarp || warp == kLoadWarpV) {
+        // ------------------------------ TMA producers ------------------------------
+        // One thread streams the K tiles (and loaded Q before), one the V tiles: with a paged cache a
+        // tile is one copy per page and 64-column half plus a block-table read per page, and a single
+        // thread issuing both rings cannot keep up with the tensor pipe at small page sizes.
         if (lane == 0) {
-            const TileInfo ts[2] = {t0, t1};
+            const bool is_v = warp == kLoadWarpV;
+            unsigned char (*ring)[kTileBytes] = is_v ? sm.v : sm.k;
+            unsigned long long* full = is_v ? sm.v_full : sm.k_full;
+            unsigned long long* empty = is_v ? sm.v_empty : sm.k_empty;
+            const CUtensorMap* map = is_v ? &v_map : &k_map;
             bool alive = true;
-            for (int j = n_pre; j < n_max && alive; ++j) {   // tiles 0 .. n_pre-1 were issued during set-up
+            int issued = is_v ? 0 : n_pre;   // K tiles 0 .. n_pre-1 were issued during set-up
+            for (int j = issued; j < n_max && alive; ++j) {
                 const int s = j % kStages;
-                const unsigned ph = (unsigned)(j / kStages) & 1u;
-                alive = mbar_wait(sm, &sm.k_empty[s], ph ^ 1u, a.status, 1);
-                if (!alive) break;
-                trace_event(trace, 2, j, 6);
-                load_kv_tile(a, sq, b, kvh, sm.k[s], &k_map, &sm.k_full[s], j);
-                alive = mbar_wait(sm, &sm.v_empty[s], ph ^ 1u, a.status, 2);
-                if (!alive) break;
-                trace_event(trace, 2, j, 7);
-                load_kv_tile(a, sq, b, kvh, sm.v[s], &v_map, &sm.v_full[s], j);
-            }
-            // Make sure none of this CTA's bulk copies is still in flight when it exits: wait
-            // (bounded) for the last fill of every stage and of the Q tiles.
-            for (int t = 0; t < 2; ++t)
-                if (ts[t].valid) mbar_wait(sm, &sm.q_full[t], 0, a.status, 3);
-            for (int s = 0; s < kStages; ++s) {
-                // last j with j % kStages == s that was actually issued
-                int last = -1;
-                for (int j = s; j < n_max; j += kStages) last = j;
-                if (last >= 0) {
-                    const unsigned ph = (unsigned)(last / kStages) & 1u;
-                    // ignore the abort flag here: these waits only depend on the copy engine
-                    const unsigned long long t_begin = global_timer_ns();
-                    while (!mbar_try_wait(&sm.k_full[s], ph) && global_timer_ns() - t_begin < 100000000ULL) {}
-                    while (!mbar_try_wait(&sm.v_full[s], ph) && global_timer_ns() - t_begin < 100000000ULL) {}
+                if (j >= kStages) {
+                    alive = mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a.status, is_v ? 2 : 1);
+                    if (!alive) break;
                 }
+                load_kv_tile(a, sq, b, kvh, ring[s], map, &full[s], j);
+                issued = j + 1;
+            }
+            // Make sure none of this thread's bulk copies is still in flight when the CTA exits: wait
+            // (bounded) for the last fill of every stage (and of the Q tiles). These waits ignore the
+            // abort flag: they only depend on the copy engine.
+            if (!is_v) {
+                if (t0.valid) mbar_wait(sm, &sm.q_full[0], 0, a.status, 3);
+                if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a.status, 3);
+            }
+            const unsigned long long t_begin = global_timer_ns();
+            for (int s = 0; s < kStages; ++s) {
+                if (issued <= s) continue;   // never filled
+                const int last = issued - 1 - (issued - 1 - s) % kStages;   // last issued tile of this stage
+                while (!mbar_try_wait(&full[s], (unsigned)(last / kStages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
             }
         }
     } else if (warp == kMmaWarp) {
