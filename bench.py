@@ -37,7 +37,7 @@ NOMINAL_HBM_GBS = 8000.0
 # the ncu captures summarised under profiles/. prefill_c2 was captured at full size; the decode
 # figure is the ratio measured on decode_c4_small (399.9 MB moved for 394.2 MB of algorithmic bytes,
 # L2 hit rate 0.4 %: traffic grows in proportion to the cached tokens) applied to the run's own bytes.
-NCU_TRAFFIC_BYTES = {"prefill_c2": 511_807_232 + 51_410_944}
+NCU_TRAFFIC_BYTES = {"prefill_c2": 512_585_728 + 51_621_632}
 NCU_DECODE_TRAFFIC_RATIO = (394_139_648 + 4_231_680) / 394_223_184
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
