@@ -231,6 +231,14 @@ __device__ __forceinline__ void tc_st32(unsigned taddr, const unsigned (&u)[32])
         "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
         : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tc_st16(unsigned taddr, const unsigned (&u)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]), "r"(u[9]),
+        "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15])
+        : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
@@ -644,87 +652,186 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const bool need_mask = (long long)(key0 + kBlockN - 1) > min((long long)sq.pos_off + ti.row0, (long long)sq.kv_len - 1);
             const int limit = need_mask ? (int)max(-1LL, min(limit_ll, (long long)kBlockN)) : kBlockN;
 
-            float sv[4][32];
+            // An aligned diagonal tile (row i of the tile sees exactly keys 0..i of it) has a fixed shape
+            // per warp: warp w sees chunks 0..w-1 of 32 columns in full, chunk w up to its own lane,
+            // nothing after it. It is handled with the chunks rotated so that the diagonal one sits in
+            // register slot 0 (the tensor-memory addresses are run-time values, the slots are not):
+            // 32 compares instead of 128, FMA-pipe exponentials in the full chunks, no work in the
+            // unseen ones. Any other masked tile (cut by the end of K/V, unaligned start) takes the
+            // general code below.
+            const bool diag_tile = need_mask && (long long)sq.pos_off + ti.row0 == (long long)key0 &&
+                                   (long long)sq.pos_off + ti.row0 + kBlockM - 1 <= (long long)sq.kv_len - 1;
+            if (diag_tile) {
+                const int w = warp & 3;
+                float dv[4][32];   // slot k holds chunk (w + k) & 3
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
-            tc_wait_ld();
-            if (need_mask) {
+                for (int k = 0; k < 4; ++k) tc_ld32(s_addr + ((w + k) & 3) * 32, dv[k]);
+                tc_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int i = 0; i < 32; ++i)
+                    if (i > lane) dv[0][i] = -INFINITY;
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i > limit) sv[c][i] = -INFINITY;
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], dv[0][i], dv[0][i + 1]);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+                for (int k = 1; k < 4; ++k) {
+                    if (((w + k) & 3) < w) {   // a chunk before the diagonal one: seen in full
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
-            trace_event(trace, t, j, 1);
-
-            float alpha = 1.0f;
-            bool changed = false;
-            if (mx > m + kRescaleThreshold) {   // also true for the first finite max (m == -inf)
-                alpha = ex2(m - mx);            // 0 when m == -inf
-                m = mx;
-                changed = true;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, changed)) {
-                // rescale this warp's 32 rows of O in tensor memory (rows that did not move use 1.0)
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    float ov[32];
-                    tc_ld32(o_addr + c * 32, ov);
-                    tc_wait_ld();
-                    unsigned ou[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) ou[i] = __float_as_uint(ov[i] * alpha);
-                    tc_st32(o_addr + c * 32, ou);
+                        for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], dv[k][i], dv[k][i + 1]);
+                    }
                 }
-            }
-            const float m_use = (m == -INFINITY) ? 0.0f : m;
-            // exp2(s * scale - m) two columns at a time: packed FMA for the argument and the row sum;
-            // one pair in four takes its exponential on the FMA pipe (unmasked tiles only), which
-            // relieves the special-function unit the two warpgroups compete for.
-            const unsigned long long scale2 = pack2(a.scale_log2, a.scale_log2);
-            const unsigned long long neg_m2 = pack2(-m_use, -m_use);
-            unsigned long long sum2 = pack2(0.0f, 0.0f);
-            // two straight-line copies (masked tiles keep every exponential on the special-function
-            // unit, where -inf gives an exact zero) rather than a branch inside the unrolled loop
-            auto exp_phase = [&](auto fma_pipe_share) {
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+                trace_event(trace, t, j, 1);
+                float alpha = 1.0f;
+                bool changed = false;
+                if (mx > m + kRescaleThreshold) {
+                    alpha = ex2(m - mx);
+                    m = mx;
+                    changed = true;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, changed)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float ov[32];
+                        tc_ld32(o_addr + c * 32, ov);
+                        tc_wait_ld();
+                        unsigned ou[32];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    unsigned pu[32];
+                        for (int i = 0; i < 32; ++i) ou[i] = __float_as_uint(ov[i] * alpha);
+                        tc_st32(o_addr + c * 32, ou);
+                    }
+                }
+                const float m_use = (m == -INFINITY) ? 0.0f : m;
+                const unsigned long long scale2 = pack2(a.scale_log2, a.scale_log2);
+                const unsigned long long neg_m2 = pack2(-m_use, -m_use);
+                unsigned long long sum2 = pack2(0.0f, 0.0f);
+                {   // the diagonal chunk: every exponential on the special-function unit (-inf gives an exact zero)
+                    unsigned pu[16];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int cc = c * 2 + (i >> 4);
-                        const int ii = (i & 15) * 2;
-                        float x0, x1, p0, p1;
-                        unpack2(fma2(pack2(sv[cc][ii], sv[cc][ii + 1]), scale2, neg_m2), x0, x1);
-                        if (decltype(fma_pipe_share)::value && (i & 3) == 3) {
-                            ex2_fma2(x0, x1, p0, p1);
-                        } else {
-                            p0 = ex2(x0);
-                            p1 = ex2(x1);
-                        }
+                    for (int i = 0; i < 16; ++i) {
+                        float x0, x1;
+                        unpack2(fma2(pack2(dv[0][2 * i], dv[0][2 * i + 1]), scale2, neg_m2), x0, x1);
+                        const float p0 = ex2(x0), p1 = ex2(x1);
                         sum2 = add2(sum2, pack2(p0, p1));
                         pu[i] = pack16<T>(p0, p1);
                     }
-                    tc_st32(s_addr + c * 32, pu);
-                    tc_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
-                    if (c == 0) trace_event(trace, t, j, 2);
+                    tc_st16(s_addr + w * 16, pu);   // P of chunk c lives in 16 packed columns at c * 16
                 }
-            };
-            if (need_mask) exp_phase(std::false_type{});
-            else exp_phase(std::true_type{});
-            float sum_lo, sum_hi;
-            unpack2(sum2, sum_lo, sum_hi);
-            const float sum = sum_lo + sum_hi;
-            l = l * alpha + sum;
+#pragma unroll
+                for (int k = 1; k < 4; ++k) {
+                    const int c = (w + k) & 3;
+                    unsigned pu[16];
+                    if (c < w) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float x0, x1, p0, p1;
+                            unpack2(fma2(pack2(dv[k][2 * i], dv[k][2 * i + 1]), scale2, neg_m2), x0, x1);
+                            if ((i & 3) == 3) {
+                                ex2_fma2(x0, x1, p0, p1);
+                            } else {
+                                p0 = ex2(x0);
+                                p1 = ex2(x1);
+                            }
+                            sum2 = add2(sum2, pack2(p0, p1));
+                            pu[i] = pack16<T>(p0, p1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) pu[i] = 0u;
+                    }
+                    tc_st16(s_addr + c * 16, pu);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.p_lo[t]);
+                trace_event(trace, t, j, 2);
+                mbar_arrive(&sm.p_hi[t]);
+                float sum_lo, sum_hi;
+                unpack2(sum2, sum_lo, sum_hi);
+                l = l * alpha + (sum_lo + sum_hi);
+            } else {
+                float sv[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
+                tc_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i > limit) sv[c][i] = -INFINITY;
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
+                trace_event(trace, t, j, 1);
+
+                float alpha = 1.0f;
+                bool changed = false;
+                if (mx > m + kRescaleThreshold) {   // also true for the first finite max (m == -inf)
+                    alpha = ex2(m - mx);            // 0 when m == -inf
+                    m = mx;
+                    changed = true;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, changed)) {
+                    // rescale this warp's 32 rows of O in tensor memory (rows that did not move use 1.0)
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float ov[32];
+                        tc_ld32(o_addr + c * 32, ov);
+                        tc_wait_ld();
+                        unsigned ou[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ou[i] = __float_as_uint(ov[i] * alpha);
+                        tc_st32(o_addr + c * 32, ou);
+                    }
+                }
+                const float m_use = (m == -INFINITY) ? 0.0f : m;
+                // exp2(s * scale - m) two columns at a time: packed FMA for the argument and the row sum;
+                // one pair in four takes its exponential on the FMA pipe (unmasked tiles only), which
+                // relieves the special-function unit the two warpgroups compete for.
+                const unsigned long long scale2 = pack2(a.scale_log2, a.scale_log2);
+                const unsigned long long neg_m2 = pack2(-m_use, -m_use);
+                unsigned long long sum2 = pack2(0.0f, 0.0f);
+                // two straight-line copies (masked tiles keep every exponential on the special-function
+                // unit, where -inf gives an exact zero) rather than a branch inside the unrolled loop
+                auto exp_phase = [&](auto fma_pipe_share) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        unsigned pu[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int cc = c * 2 + (i >> 4);
+                            const int ii = (i & 15) * 2;
+                            float x0, x1, p0, p1;
+                            unpack2(fma2(pack2(sv[cc][ii], sv[cc][ii + 1]), scale2, neg_m2), x0, x1);
+                            if (decltype(fma_pipe_share)::value && (i & 3) == 3) {
+                                ex2_fma2(x0, x1, p0, p1);
+                            } else {
+                                p0 = ex2(x0);
+                                p1 = ex2(x1);
+                            }
+                            sum2 = add2(sum2, pack2(p0, p1));
+                            pu[i] = pack16<T>(p0, p1);
+                        }
+                        tc_st32(s_addr + c * 32, pu);
+                        tc_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
+                        if (c == 0) trace_event(trace, t, j, 2);
+                    }
+                };
+                if (need_mask) exp_phase(std::false_type{});
+                else exp_phase(std::true_type{});
+                float sum_lo, sum_hi;
+                unpack2(sum2, sum_lo, sum_hi);
+                const float sum = sum_lo + sum_hi;
+                l = l * alpha + sum;
+            }
             trace_event(trace, t, j, 3);
         }
 
