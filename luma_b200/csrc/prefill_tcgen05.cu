@@ -161,20 +161,12 @@ __device__ __forceinline__ void tc_commit(unsigned long long* bar) {
     asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void tc_mma_ss(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // The products as the issuer warp runs them: the whole warp executes the instruction stream
 // converged and one elected lane issues. Keeping the warp uniform lets the descriptors live in
 // uniform registers, so a product costs a handful of issue slots; issued from a single diverged
 // lane each needs register-to-uniform moves and, next to ALU-heavy warps on the same scheduler,
 // took ~130 clocks instead of the tensor pipe's 64. The accumulate flag is a compile-time constant.
+// D[tmem] (+)= A[smem] * B[smem]
 template <bool kAccumulate>
 __device__ __forceinline__ void tc_mma_ss_imm(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc, unsigned idesc) {
     if (kAccumulate)
@@ -186,6 +178,7 @@ __device__ __forceinline__ void tc_mma_ss_imm(unsigned d_tmem, unsigned long lon
                      "l"(a_desc), "l"(b_desc), "r"(idesc)
                      : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]
 template <bool kAccumulate>
 __device__ __forceinline__ void tc_mma_ts_imm(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc) {
     if (kAccumulate)
@@ -197,16 +190,6 @@ __device__ __forceinline__ void tc_mma_ts_imm(unsigned d_tmem, unsigned a_tmem, 
                      "r"(a_tmem), "l"(b_desc), "r"(idesc)
                      : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void tc_mma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned idesc,
-                                          unsigned accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp <-> TMEM lane (base + i)
 __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&r)[32]) {
     unsigned* u = reinterpret_cast<unsigned*>(r);
