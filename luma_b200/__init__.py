@@ -7,6 +7,9 @@ Layers, named after the reference's modules (luma-flash-attn/src/api/):
           flash_attn_with_kvcache (high.rs)
   error — FlashAttnError hierarchy (error.rs)
   dist  — head-sharded attention + output all-gather (luma-dist Comm::all_gather)
+  functional — the Math / Flash dispatcher of luma-nn (functional/attention.rs); Math is the
+          reference's portable tensor-op path, chosen only when the caller names it — Flash
+          never falls back to it
 
 There is no CPU implementation behind any of these: importing `ffi` without a built
 libflash_attn.so raises, and every compute call needs a CUDA device.
