@@ -1,8 +1,11 @@
 // Causal, GQA-capable flash-attention prefill forward for sm_100a: TMA-fed Q/K/V tiles,
 // tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
 // warp-specialised roles. Handles f16/bf16 storage with head_size 128, no padding mask, for the
-// batched entry point. Replaces flash_attn_kernel (luma-flash-attn/kernels/flash_attn_func.cu:29-226),
-// a one-thread-per-query-row scalar kernel.
+// batched entry point, chunked prefill over a paged cache, and the packed varlen entry point when
+// the caller gives the packed buffers' row counts. Replaces flash_attn_kernel
+// (luma-flash-attn/kernels/flash_attn_func.cu:29-226), flash_attn_prefill_kernel
+// (kernels/flash_attn_with_kvcache.cu:157-277) and flash_attn_varlen_kernel
+// (kernels/flash_attn_varlen_func.cu:35-199), one-thread-per-query-row scalar kernels.
 //
 // One CTA (384 threads, 1 per SM) owns up to two query tiles of 128 rows that share a batch
 // element and a KV head — two query heads of one GQA group at the same row block, or two
@@ -12,10 +15,13 @@
 //                     from tensor memory (tcgen05.ld), running max / sum in registers (exp2 with
 //                     the scale folded in), write P as packed 16-bit back over S (tcgen05.st),
 //                     rescale O in tensor memory only when the row max moved by more than 2^8,
-//                     final normalisation and store of O (and LSE)
+//                     final normalisation of O, staged in Q's shared memory and written with bulk
+//                     tensor stores (and LSE); setmaxnreg gives these warps 208 registers
+//   warp 11         : idle (completes the third warpgroup for setmaxnreg)
 //   warp 8 / 10     : TMA producers — warp 8 loads Q once, then the K tiles; warp 10 the V tiles; two 2-stage rings
 //   warp 9          : MMA issuer — S_t = Q_t K^T (SS form), O_t += P_t V (P from tensor memory),
-//                     completion signalled with tcgen05.commit on mbarriers
+//                     completion signalled with tcgen05.commit on mbarriers; the warp runs converged
+//                     and one elected lane issues
 // While one warpgroup runs its softmax the tensor core works on the other tile.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t aliases S_t.
 // Shared memory: Q 2 x 32 KiB, K ring 2 x 32 KiB, V ring 2 x 32 KiB, all 128-byte swizzled
