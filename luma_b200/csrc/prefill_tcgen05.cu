@@ -17,11 +17,11 @@
 //                     rescale O in tensor memory only when the row max moved by more than 2^8,
 //                     final normalisation of O, staged in Q's shared memory and written with bulk
 //                     tensor stores (and LSE); setmaxnreg gives these warps 208 registers
-//   warp 11         : idle (completes the third warpgroup for setmaxnreg)
 //   warp 8 / 10     : TMA producers — warp 8 loads Q once, then the K tiles; warp 10 the V tiles; two 2-stage rings
 //   warp 9          : MMA issuer — S_t = Q_t K^T (SS form), O_t += P_t V (P from tensor memory),
 //                     completion signalled with tcgen05.commit on mbarriers; the warp runs converged
 //                     and one elected lane issues
+//   warp 11         : idle (completes the third warpgroup, which setmaxnreg needs whole)
 // While one warpgroup runs its softmax the tensor core works on the other tile.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t aliases S_t.
 // Shared memory: Q 2 x 32 KiB, K ring 2 x 32 KiB, V ring 2 x 32 KiB, all 128-byte swizzled
