@@ -325,6 +325,33 @@ def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d,
     }
 
 
+def run_softmax(torch, low, ffi, dev, name, rows, n, dtype_name, steps, warmup, peaks, seed):
+    """Row softmax of the math path on a (rows, n) score matrix: HBM-bound, one read and one write."""
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype_name]
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    x = (torch.randn(rows, n, generator=g, device=dev, dtype=torch.float32) * 2.0).to(dt)
+    y = torch.empty_like(x)
+
+    def step():
+        low.softmax_last_dim(x, out=y)
+
+    step()
+    path, launches = ffi.last_path(), ffi.last_launches()
+    sec = time_steps(torch, step, steps, warmup)
+    nbytes = 2 * rows * n * x.element_size()
+    gbs = nbytes * steps / sec / 1e9
+    return {
+        "metric": "row-softmax HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
+        "kernel_path": path, "launches_per_step": launches,
+        "config": {"workload": name, "rows": rows, "row_size": n, "dtype": dtype_name, "bytes_per_step": nbytes,
+                   "l2_policy": "inputs larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth)",
+                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS},
+    }
+
+
 NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool (nominal 900)
 
 
@@ -557,6 +584,10 @@ def main():
                                  scale_in=0.5, want_lse=False)
         elif name == "varlen_prefill":
             res = run_varlen_prefill(torch, low, ffi, dev, name, 32, 1024, 8192, 32, 8, 128, args.steps, args.warmup, peaks, seed=7)
+        elif name.startswith("softmax_"):   # softmax_<dtype>_<rows>x<row_size>, e.g. softmax_bf16_131072x4096
+            _, dtn, shp = name.split("_")
+            r_, n_ = (int(t) for t in shp.split("x"))
+            res = run_softmax(torch, low, ffi, dev, name, r_, n_, dtn, args.steps, args.warmup, peaks, seed=8)
         elif name == "decode_c4":
             res, _ = run_decode(torch, low, ffi, dev, name, 64, 32, 8, 128, 16, 512, 8192, 40000, args.steps, args.warmup,
                                 peaks, seed=4)
@@ -664,6 +695,11 @@ def main():
             # not a BASELINE config: 32 prompts of 1024..8192 tokens packed, GQA 32/8 (q+k+v+o = 230 MB at the mean)
             workloads["varlen_prefill"] = run_varlen_prefill(torch, low, ffi, dev, "varlen_prefill", 32, 1024, 8192, 32, 8, 128,
                                                              extra_steps, 3, peaks, seed=7)
+            torch.cuda.empty_cache()
+        if only in (None, "softmax_scores"):
+            # not a BASELINE config: the scores of one configs[2]-sized head group on the math path, bf16
+            workloads["softmax_scores"] = run_softmax(torch, low, ffi, dev, "softmax_scores", 131072, 4096, "bf16",
+                                                      extra_steps, 3, peaks, seed=8)
             torch.cuda.empty_cache()
         if only in (None, "decode_c4"):
             workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,

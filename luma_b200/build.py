@@ -18,7 +18,7 @@ CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libflash_attn.so"
 
-SOURCES = ["api.cu", "tile_simt.cu", "decode_splitk.cu", "prefill_tcgen05.cu", "kv_append.cu"]
+SOURCES = ["api.cu", "tile_simt.cu", "decode_splitk.cu", "prefill_tcgen05.cu", "kv_append.cu", "softmax_lastdim.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -39,9 +39,14 @@ EXPORTED_SYMBOLS = (
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
     + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather",
        "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total"]
+    + [f"luma_softmax_{s}" for s in DTYPE_SUFFIX]   # include/luma_nn_kernels.h
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
 )
+
+for _s in DTYPE_SUFFIX:
+    getattr(lib, f"luma_softmax_{_s}").argtypes = [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_void_p]
+    getattr(lib, f"luma_softmax_{_s}").restype = c_int
 
 _VARLEN_TOTAL_ARGS = _VARLEN_ARGS[:-1] + [c_int, c_int, c_void_p]
 for _s in ("f16", "bf16"):

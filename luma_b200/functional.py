@@ -87,7 +87,13 @@ def _math_path(q, k, v, scale, causal, start_pos):
         gpos = torch.arange(sq, device=q.device).unsqueeze(1) + int(start_pos)   # causal_mask (attention.rs:112-127)
         keys = torch.arange(skv, device=q.device).unsqueeze(0)
         scores = scores.masked_fill(keys > gpos, float("-inf"))
-    probs = torch.softmax(scores, dim=-1)
+    if scores.is_cuda and not (torch.is_grad_enabled() and scores.requires_grad):
+        # inference on a GPU: this library's row-softmax kernel (the reference's CUDA math path runs
+        # luma-cuda's softmax_f32 here); with autograd on, torch's differentiable softmax
+        from . import low
+        probs = low.softmax_last_dim(scores.contiguous(), out=None)
+    else:
+        probs = torch.softmax(scores, dim=-1)
     out = torch.matmul(probs, vf).permute(0, 2, 1, 3)
     return out.to(q.dtype).contiguous()
 

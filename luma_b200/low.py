@@ -182,3 +182,21 @@ def kvcache_append(k_new, v_new, k_cache, v_cache, block_tables, context_lens, n
         num_seqs, n_new, kv_heads, head_size, k_new.element_size(), block_size, max_blocks,
         _stream_ptr(stream, k_new))
     E.from_status(code, ffi.last_error())
+
+
+def softmax_last_dim(x, out=None, stream=None):
+    """Softmax over the last dimension of a dense device tensor (f32 / f16 / bf16), f32 arithmetic;
+    the role of luma-cuda's softmax_<T> kernels (luma-cuda/kernels/nn.cu:21-76, launched from
+    luma-cuda/src/ops/nn_provide.rs:10-70) on the math path. `out` may be `x` itself."""
+    if not x.is_contiguous():
+        raise E.Unsupported("softmax_last_dim: the input must be contiguous (nn_provide.rs:11-13)")
+    if out is None:
+        out = torch.empty_like(x)
+    elif tuple(out.shape) != tuple(x.shape) or out.dtype != x.dtype or not out.is_contiguous():
+        raise E.InvalidShape("softmax_last_dim: out must be contiguous and shaped and typed like the input")
+    n = x.shape[-1] if x.dim() > 0 else 1
+    rows = x.numel() // n if n > 0 else 0
+    code = getattr(ffi.lib, f"luma_softmax_{_suffix(x)}")(_ptr(x), _ptr(out), rows, n, _stream_ptr(stream, x))
+    E.from_status(code, ffi.last_error())
+    return out
+

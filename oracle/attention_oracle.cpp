@@ -297,4 +297,18 @@ int oracle_hardware_threads(void) {
     return n == 0 ? 1 : static_cast<int>(n);
 }
 
+
+// Row softmax over the last dimension of a dense (rows, n) f32 matrix with luma-cpu's own routine
+// (luma-cpu/src/kernels/nn.rs:10-56: contiguous last-dim case -> online_softmax per row).
+int oracle_softmax_last_dim_f32(const float* in, float* out, long long rows, int n) {
+    if (in == nullptr || out == nullptr || rows < 0 || n < 0) return 1;
+    for (long long r = 0; r < rows; ++r) {
+        float* row = out + r * n;
+        for (int i = 0; i < n; ++i) row[i] = in[r * n + i];
+        float m = 0.0f, s = 0.0f;
+        online_softmax_f32(row, n, &m, &s);
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -87,6 +87,19 @@ def sdpa_math_f32(q, k, v, scale=None, causal=True, start_pos=0, nthreads=None, 
     return (o, lse) if return_lse else o
 
 
+def softmax_last_dim_f32(x):
+    """Row softmax over the last dimension with luma-cpu's online softmax, f32 (any leading shape)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[-1]
+    rows = x.size // n if n else 0
+    out = np.empty_like(x)
+    _lib.oracle_softmax_last_dim_f32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int]
+    _lib.oracle_softmax_last_dim_f32.restype = ctypes.c_int
+    if _lib.oracle_softmax_last_dim_f32(_p(x), _p(out), rows, n) != 0:
+        raise ValueError("oracle_softmax_last_dim_f32: bad arguments")
+    return out
+
+
 def _attn_f64(q, k, v, q_start, q_len, kv_start, kv_len, pos_off, Hq, Hkv, D, scale,
               block_tables=None, max_blocks=0, block_size=0, mask=None, mask_stride=0,
               nthreads=None, return_lse=False):
