@@ -5,8 +5,9 @@
 // reduced in f32 (running max and sum merged across lanes with the online-softmax rule of
 // luma-cpu/src/kernels/nn.rs:39-56) and written once, rounded to nearest even: the kernel is bound
 // by HBM at 2 * rows * row_size * sizeof(T) bytes.
-//   rows of up to 32*16 vectors  : one warp per row (several short rows at a time), no shared memory
-//   rows of up to 512*8 vectors  : one CTA of 128 / 256 / 512 threads per row, 8 vectors per thread
+// 32 elements per thread throughout (4 vectors of 16-bit storage, 8 of f32):
+//   rows of up to 1024 elements  : one warp per row (several short rows at a time), no shared memory
+//   rows of up to 32768 elements : one CTA of 64 .. 1024 threads per row, one shared-memory exchange
 //   longer or unaligned rows     : one CTA per row, two passes over the row (read twice)
 #include "common.cuh"
 #include "../../include/luma_nn_kernels.h"
@@ -37,6 +38,12 @@ __device__ __forceinline__ void store_vec(T* p, const float (&x)[VecOf<T>::n]) {
     *reinterpret_cast<uint4*>(p) = raw;
 }
 
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // (m, s) = running max and sum of exp(x - m); merging two partial results
 __device__ __forceinline__ void merge(float& m, float& s, float m2, float s2) {
     const float mn = fmaxf(m, m2);
@@ -55,8 +62,18 @@ __device__ __forceinline__ void warp_merge(float& m, float& s) {
     }
 }
 
-// One warp works on R rows at a time, each row in VPT vectors per lane (R * VPT = 8 or 16 vectors,
-// i.e. 128-256 bytes, in flight per lane).
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// One warp works on R rows at a time, each row in VPT vectors per lane (R * VPT vectors = 32 elements per lane).
 template <typename T, int VPT, int R>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int n) {
     constexpr int V = VecOf<T>::n;
@@ -88,19 +105,20 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__
 #pragma unroll
             for (int i = 0; i < V; ++i) m[r] = fmaxf(m[r], x[r][v][i]);
         float s = 0.0f;
-        const float ml = m[r] * kLog2e;
+        const float ml = m[r] == -INFINITY ? 0.0f : m[r] * kLog2e;   // a lane that saw only -inf: exp2(-inf) = 0
 #pragma unroll
         for (int v = 0; v < VPT; ++v)
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                x[r][v][i] = m[r] == -INFINITY ? 0.0f : exp2f(fmaf(x[r][v][i], kLog2e, -ml));   // exp(x - m_lane)
+                x[r][v][i] = fast_ex2(fmaf(x[r][v][i], kLog2e, -ml));   // exp(x - m_lane)
                 s += x[r][v][i];
             }
-        float mr = m[r], sr = s;
-        warp_merge(mr, sr);
-        // exp(x - m_row) / s_row = exp(x - m_lane) * exp(m_lane - m_row) / s_row; a row of -inf only gives NaN
-        // (as the reference's arithmetic does)
-        const float f = (m[r] == -INFINITY && mr != -INFINITY) ? 0.0f : exp2f((m[r] - mr) * kLog2e) / sr;
+        // exp(x - m_row) / s_row = exp(x - m_lane) * exp(m_lane - m_row) / s_row: the row max first, then
+        // every lane's sum rescaled once; a row of -inf only gives NaN (as the reference's arithmetic does)
+        const float mr = warp_max(m[r]);
+        const float rescale = (m[r] == -INFINITY && mr != -INFINITY) ? 0.0f : fast_ex2((m[r] - mr) * kLog2e);
+        const float sr = warp_sum(s * rescale);
+        const float f = rescale / sr;
         if (row0 + r < rows) {
             T* dst = out + (row0 + r) * n;
 #pragma unroll
@@ -141,22 +159,25 @@ __global__ void __launch_bounds__(THREADS) softmax_block_kernel(const T* __restr
 #pragma unroll
         for (int i = 0; i < V; ++i) m = fmaxf(m, x[v][i]);
     float s = 0.0f;
-    const float ml = m * kLog2e;
+    const float ml = m == -INFINITY ? 0.0f : m * kLog2e;   // a thread that saw only -inf: exp2(-inf) = 0
 #pragma unroll
     for (int v = 0; v < VPT; ++v)
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            x[v][i] = m == -INFINITY ? 0.0f : exp2f(fmaf(x[v][i], kLog2e, -ml));
+            x[v][i] = fast_ex2(fmaf(x[v][i], kLog2e, -ml));
             s += x[v][i];
         }
-    float mr = m, sr = s;
-    warp_merge(mr, sr);
-    if (lane == 0) { sh_m[warp] = mr; sh_s[warp] = sr; }
+    // row max through shared memory, every thread's sum rescaled once, then the row sum
+    float mw = warp_max(m);
+    if (lane == 0) sh_m[warp] = mw;
     __syncthreads();
-    mr = lane < THREADS / 32 ? sh_m[lane] : -INFINITY;
-    sr = lane < THREADS / 32 ? sh_s[lane] : 0.0f;
-    warp_merge(mr, sr);
-    const float f = (m == -INFINITY && mr != -INFINITY) ? 0.0f : exp2f((m - mr) * kLog2e) / sr;
+    const float mr = warp_max(lane < THREADS / 32 ? sh_m[lane] : -INFINITY);
+    const float rescale = (m == -INFINITY && mr != -INFINITY) ? 0.0f : fast_ex2((m - mr) * kLog2e);
+    const float sw = warp_sum(s * rescale);
+    if (lane == 0) sh_s[warp] = sw;
+    __syncthreads();
+    const float sr = warp_sum(lane < THREADS / 32 ? sh_s[lane] : 0.0f);
+    const float f = rescale / sr;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
         const int col = (v * THREADS + threadIdx.x) * V;
@@ -190,7 +211,7 @@ __global__ void __launch_bounds__(kStreamThreads) softmax_stream_kernel(const T*
         if (mv == -INFINITY) continue;
         float sv = 0.0f;
 #pragma unroll
-        for (int i = 0; i < V; ++i) sv += exp2f((x[i] - mv) * kLog2e);
+        for (int i = 0; i < V; ++i) sv += fast_ex2((x[i] - mv) * kLog2e);
         merge(m, s, mv, sv);
     }
     warp_merge(m, s);
@@ -205,7 +226,7 @@ __global__ void __launch_bounds__(kStreamThreads) softmax_stream_kernel(const T*
         if (VEC) load_vec<T>(src + c, x);
         else x[0] = to_f32<T>(src[c]);
 #pragma unroll
-        for (int i = 0; i < V; ++i) x[i] = exp2f(fmaf(x[i], kLog2e, -ml)) * inv;
+        for (int i = 0; i < V; ++i) x[i] = fast_ex2(fmaf(x[i], kLog2e, -ml)) * inv;
         if (VEC) store_vec<T>(dst + c, x);
         else dst[c] = from_f32<T>(x[0]);
     }
@@ -214,27 +235,32 @@ __global__ void __launch_bounds__(kStreamThreads) softmax_stream_kernel(const T*
 template <typename T>
 int launch_softmax(const T* in, T* out, long long rows, int n, cudaStream_t stream) {
     constexpr int V = VecOf<T>::n;
+    // 32 elements per thread (4 vectors of 16-bit, 8 of f32): few enough registers for 4 CTAs of 256
+    // threads per SM, whose loads, arithmetic and stores then overlap; with 128 elements per thread
+    // (one resident CTA) a bf16 row of 4096 reached 0.54 of the copy bandwidth
+    constexpr int P = 32 / V;
     const bool aligned = (n % V) == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     const int vecs = (n + V - 1) / V;
     const int warps = 8;
     auto warp_grid = [&](int r) { return (unsigned)((rows + (long long)warps * r - 1) / ((long long)warps * r)); };
-    if (aligned && vecs <= 32 * 16) {
+    const unsigned grid = (unsigned)rows;
+    if (aligned && vecs <= 32 * P) {
         const int vpt = (vecs + 31) / 32;
-        if (vpt <= 1) softmax_warp_kernel<T, 1, 8><<<warp_grid(8), warps * 32, 0, stream>>>(in, out, rows, n);
-        else if (vpt <= 2) softmax_warp_kernel<T, 2, 4><<<warp_grid(4), warps * 32, 0, stream>>>(in, out, rows, n);
-        else if (vpt <= 4) softmax_warp_kernel<T, 4, 2><<<warp_grid(2), warps * 32, 0, stream>>>(in, out, rows, n);
-        else if (vpt <= 8) softmax_warp_kernel<T, 8, 1><<<warp_grid(1), warps * 32, 0, stream>>>(in, out, rows, n);
-        else softmax_warp_kernel<T, 16, 1><<<warp_grid(1), warps * 32, 0, stream>>>(in, out, rows, n);
+        if (vpt <= 1) softmax_warp_kernel<T, 1, P><<<warp_grid(P), warps * 32, 0, stream>>>(in, out, rows, n);
+        else if (vpt <= 2) softmax_warp_kernel<T, 2, P / 2><<<warp_grid(P / 2), warps * 32, 0, stream>>>(in, out, rows, n);
+        else if (vpt <= 4) softmax_warp_kernel<T, 4, P / 4><<<warp_grid(P / 4), warps * 32, 0, stream>>>(in, out, rows, n);
+        else softmax_warp_kernel<T, P, 1><<<warp_grid(1), warps * 32, 0, stream>>>(in, out, rows, n);
         note_path("softmax_warp", 1);
-    } else if (aligned && vecs <= 512 * 8) {
-        const unsigned grid = (unsigned)rows;
-        if (vecs <= 128 * 8) softmax_block_kernel<T, 8, 128><<<grid, 128, 0, stream>>>(in, out, n);
-        else if (vecs <= 256 * 8) softmax_block_kernel<T, 8, 256><<<grid, 256, 0, stream>>>(in, out, n);
-        else softmax_block_kernel<T, 8, 512><<<grid, 512, 0, stream>>>(in, out, n);
+    } else if (aligned && vecs <= 1024 * P) {
+        if (vecs <= 64 * P) softmax_block_kernel<T, P, 64><<<grid, 64, 0, stream>>>(in, out, n);
+        else if (vecs <= 128 * P) softmax_block_kernel<T, P, 128><<<grid, 128, 0, stream>>>(in, out, n);
+        else if (vecs <= 256 * P) softmax_block_kernel<T, P, 256><<<grid, 256, 0, stream>>>(in, out, n);
+        else if (vecs <= 512 * P) softmax_block_kernel<T, P, 512><<<grid, 512, 0, stream>>>(in, out, n);
+        else softmax_block_kernel<T, P, 1024><<<grid, 1024, 0, stream>>>(in, out, n);
         note_path("softmax_block", 1);
     } else {
-        if (aligned) softmax_stream_kernel<T, true><<<(unsigned)rows, kStreamThreads, 0, stream>>>(in, out, n);
-        else softmax_stream_kernel<T, false><<<(unsigned)rows, kStreamThreads, 0, stream>>>(in, out, n);
+        if (aligned) softmax_stream_kernel<T, true><<<grid, kStreamThreads, 0, stream>>>(in, out, n);
+        else softmax_stream_kernel<T, false><<<grid, kStreamThreads, 0, stream>>>(in, out, n);
         note_path("softmax_stream", 1);
     }
     return check_launch("softmax_last_dim");

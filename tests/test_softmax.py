@@ -24,7 +24,7 @@ def test_oracle_softmax_matches_f64_formula():
     assert np.all(got[3, 10:] == 0.0) and abs(got[3].sum() - 1.0) < 1e-6
 
 
-# (rows, row_size): 8..2048 f32 / 4096 16-bit -> warp kernel; up to 16384 / 32768 -> CTA kernel; beyond or unaligned -> two-pass
+# (rows, row_size): up to 1024 -> warp kernel; up to 32768 -> CTA kernel; beyond or unaligned -> two-pass
 SHAPES = [(64, 8), (33, 256), (5, 1000), (17, 2048), (9, 4096), (3, 16384), (2, 40000), (7, 1001), (4, 77), (2, 33000)]
 
 
