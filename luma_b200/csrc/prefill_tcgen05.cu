@@ -1,6 +1,7 @@
 // Causal, GQA-capable flash-attention prefill forward for sm_100a: TMA-fed Q/K/V tiles,
 // tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
-// warp-specialised roles. Handles f16/bf16 storage with head_size 128, no padding mask, for the
+// warp-specialised roles. Handles f16/bf16 storage with head_size 64 or 128 (template parameter D;
+// the layout comments below give the D = 128 figures), no padding mask, for the
 // batched entry point, chunked prefill over a paged cache, and the packed varlen entry point when
 // the caller gives the packed buffers' row counts. Replaces flash_attn_kernel
 // (luma-flash-attn/kernels/flash_attn_func.cu:29-226), flash_attn_prefill_kernel
@@ -44,20 +45,21 @@ namespace {
 
 constexpr int kBlockM = 128;   // query rows per tile
 constexpr int kBlockN = 128;   // keys per K/V tile
-constexpr int kD = 128;        // head size
+// head size D (64 or 128) is a template parameter of the kernel
 constexpr int kStages = 2;     // K ring and V ring depth
 constexpr int kThreads = 384;   // three warpgroups: softmax 0, softmax 1, and producer + issuer (+ two idle warps)
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kLoadWarpV = 10;   // V-ring producer (K ring and Q: kLoadWarp)
-constexpr int kTileBytes = kBlockN * kD * 2;        // 32 KiB: two 64-column halves of 128 rows x 128 B
-constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kHalfBytes = kBlockN * 64 * 2;   // 16 KiB: one 64-column half, 128 rows x 128 B
+template <int D> struct TileBytes { static constexpr int value = kBlockN * D * 2; };   // one half at D = 64, two at D = 128
 constexpr float kRescaleThreshold = 8.0f;            // log2 units
 
+template <int D>
 struct SharedStorage {
-    alignas(1024) unsigned char q[2][kTileBytes];
-    alignas(1024) unsigned char k[kStages][kTileBytes];
-    alignas(1024) unsigned char v[kStages][kTileBytes];
+    alignas(1024) unsigned char q[2][TileBytes<D>::value];
+    alignas(1024) unsigned char k[kStages][TileBytes<D>::value];
+    alignas(1024) unsigned char v[kStages][TileBytes<D>::value];
     alignas(8) unsigned long long q_full[2];
     unsigned long long k_full[kStages], k_empty[kStages];
     unsigned long long v_full[kStages], v_empty[kStages];
@@ -126,7 +128,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Bounded wait. Returns false when the wait was abandoned (time limit, or another thread of the
 // CTA already gave up); the caller then falls through to the end of the kernel.
-__device__ __forceinline__ bool mbar_wait(SharedStorage& sm, unsigned long long* bar, unsigned parity, int* status,
+template <typename Storage>
+__device__ __forceinline__ bool mbar_wait(Storage& sm, unsigned long long* bar, unsigned parity, int* status,
                                           int where) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
@@ -305,18 +308,18 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsi
     return d;
 }
 
-// Instruction descriptor, kind::f16: f32 accumulate, A/B both f16 or both bf16, M = 128, N = 128.
+// Instruction descriptor, kind::f16: f32 accumulate, A/B both f16 or both bf16, M = 128, N = n.
 //   bits [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   bit 15 A major, bit 16 B major (0 = K-major, 1 = MN-major)  [17,23) N >> 3  [24,29) M >> 4
 template <typename T>
-__device__ __forceinline__ unsigned make_idesc(bool b_mn_major) {
+__device__ __forceinline__ unsigned make_idesc(bool b_mn_major, int n) {
     const unsigned fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     unsigned d = 0;
     d |= 1u << 4;
     d |= fmt << 7;
     d |= fmt << 10;
     d |= (b_mn_major ? 1u : 0u) << 16;
-    d |= (unsigned)(kBlockN >> 3) << 17;
+    d |= (unsigned)(n >> 3) << 17;
     d |= (unsigned)(kBlockM >> 4) << 24;
     return d;
 }
@@ -375,17 +378,18 @@ __device__ __forceinline__ TileInfo tile_info(const SeqExtent& a, int pair, int 
     return ti;
 }
 
-// One K or V tile (128 keys x 128 dims, two 64-column halves) of sequence s, tile index j.
+// One K or V tile (128 keys x D dims, D / 64 halves of 64 columns) of sequence s, tile index j.
 //   contiguous: two boxes of 128 rows starting at the sequence's row kv_crow + 128 j;
 //   paged     : one box per page and half (block_size rows), the page looked up in the block
 //               table; pages past the sequence's last one are requested at block -1, which is out
 //               of range for the tensor map and therefore arrives as zeros.
+template <int D>
 __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExtent& sq, int s, int kvh, unsigned char* dst,
                                              const CUtensorMap* map, unsigned long long* bar, int j) {
-    mbar_expect_tx(bar, kTileBytes);
+    mbar_expect_tx(bar, TileBytes<D>::value);
     if (!a.paged) {
         tma_load_4d(dst, map, bar, 0, kvh, sq.kv_crow + j * kBlockN, sq.kv_cb);
-        tma_load_4d(dst + kHalfBytes, map, bar, 64, kvh, sq.kv_crow + j * kBlockN, sq.kv_cb);
+        if (D == 128) tma_load_4d(dst + kHalfBytes, map, bar, 64, kvh, sq.kv_crow + j * kBlockN, sq.kv_cb);
     } else {
         const int bs = a.block_size;
         const int per_tile = kBlockN / bs;
@@ -394,17 +398,18 @@ __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExte
             const int pg = j * per_tile + i;
             const int blk = pg < n_pages ? a.block_tables[(long long)s * a.max_blocks + pg] : -1;
             tma_load_4d(dst + i * bs * 128, map, bar, 0, kvh, 0, blk);
-            tma_load_4d(dst + kHalfBytes + i * bs * 128, map, bar, 64, kvh, 0, blk);
+            if (D == 128) tma_load_4d(dst + kHalfBytes + i * bs * 128, map, bar, 64, kvh, 0, blk);
         }
     }
 }
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map, const PrefillArgs a) {
     extern __shared__ unsigned char smem_raw[];
-    SharedStorage& sm = *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Storage = SharedStorage<D>;
+    Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const long long t_entry = clock64();
     const unsigned long long ns_entry = a.cta_log != nullptr ? global_timer_ns() : 0ULL;
 
@@ -453,12 +458,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         auto load_q = [&](const TileInfo& ti, int t) {
             if (!ti.valid) return;
-            mbar_expect_tx(&sm.q_full[t], kTileBytes);
+            mbar_expect_tx(&sm.q_full[t], TileBytes<D>::value);
             tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ti.head, sq.q_crow + ti.row0, sq.q_cb);
-            tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, sq.q_crow + ti.row0, sq.q_cb);
+            if (D == 128) tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, sq.q_crow + ti.row0, sq.q_cb);
         };
         auto load_kv = [&](unsigned char* dst, const CUtensorMap* map, unsigned long long* bar, int j) {
-            load_kv_tile(a, sq, b, kvh, dst, map, bar, j);
+            load_kv_tile<D>(a, sq, b, kvh, dst, map, bar, j);
         };
         load_q(t0, 0);
         if (n_pre > 0) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
@@ -497,7 +502,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         // thread issuing both rings cannot keep up with the tensor pipe at small page sizes.
         if (lane == 0) {
             const bool is_v = warp == kLoadWarpV;
-            unsigned char (*ring)[kTileBytes] = is_v ? sm.v : sm.k;
+            unsigned char (*ring)[TileBytes<D>::value] = is_v ? sm.v : sm.k;
             unsigned long long* full = is_v ? sm.v_full : sm.k_full;
             unsigned long long* empty = is_v ? sm.v_empty : sm.k_empty;
             const CUtensorMap* map = is_v ? &v_map : &k_map;
@@ -509,7 +514,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     alive = mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a.status, is_v ? 2 : 1);
                     if (!alive) break;
                 }
-                load_kv_tile(a, sq, b, kvh, ring[s], map, &full[s], j);
+                load_kv_tile<D>(a, sq, b, kvh, ring[s], map, &full[s], j);
                 issued = j + 1;
             }
             // Make sure none of this thread's bulk copies is still in flight when the CTA exits: wait
@@ -529,8 +534,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer ------------------------------
         {   // the whole warp runs this block converged (see tc_mma_ss_imm)
-            const unsigned idesc_qk = make_idesc<T>(false);
-            const unsigned idesc_pv = make_idesc<T>(true);
+            const unsigned idesc_qk = make_idesc<T>(false, kBlockN);
+            const unsigned idesc_pv = make_idesc<T>(true, D);   // N = head size
             const TileInfo ts[2] = {t0, t1};
             bool alive = true;
             // Descriptors are built once; inside the loops an MMA costs one 64-bit add per operand. A
@@ -541,12 +546,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const unsigned long long dv[2] = {make_desc(smem_u32(sm.v[0]), kHalfBytes, 1024), make_desc(smem_u32(sm.v[1]), kHalfBytes, 1024)};
             static_assert(kStages == 2, "descriptor tables above hold two stages");
             auto issue_s = [&](int t, int stage) {
-                // S_t = Q_t K^T : 8 K-steps of 16 over d; both operands K-major, 128 B swizzle
+                // S_t = Q_t K^T : D / 16 K-steps over d; both operands K-major, 128 B swizzle
                 const unsigned long long qd = t ? dq[1] : dq[0];
                 const unsigned long long kd = stage ? dk[1] : dk[0];
                 const unsigned d_tmem = tmem + t * 128;
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {
+                for (int kk = 0; kk < D / 16; ++kk) {
                     const unsigned long long inc = (unsigned long long)(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
                     if (kk == 0) tc_mma_ss_imm<false>(d_tmem, qd + inc, kd + inc, idesc_qk);
                     else tc_mma_ss_imm<true>(d_tmem, qd + inc, kd + inc, idesc_qk);
@@ -680,7 +685,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
                 if (j > 0 && __any_sync(0xffffffffu, changed)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < D / 32; ++c) {
                         float ov[32];
                         tc_ld32(o_addr + c * 32, ov);
                         tc_wait_ld();
@@ -769,7 +774,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (j > 0 && __any_sync(0xffffffffu, changed)) {
                     // rescale this warp's 32 rows of O in tensor memory (rows that did not move use 1.0)
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < D / 32; ++c) {
                         float ov[32];
                         tc_ld32(o_addr + c * 32, ov);
                         tc_wait_ld();
@@ -838,23 +843,23 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (bulk_ok) {
                 // Single output: the rows go out as bulk tensor stores. Each warp lays its 32 rows down in
                 // the Q tile's shared memory (every MMA that read Q_t has finished) in the 128-byte-swizzled
-                // box layout and one lane issues two stores of 32 rows x 64 columns. Plain 16-byte stores
+                // box layout and one lane issues one store of 32 rows x 64 columns per half. Plain 16-byte stores
                 // of 32 different rows per instruction would fill the SM's memory pipeline for thousands
                 // of clocks and hold up the barrier traffic of the other tile's last steps. Rows past the
                 // end of the sequence are outside the tensor map and are not written.
-                float ov[4][32];
+                float ov[D / 32][32];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tc_ld32(o_addr + c * 32, ov[c]);
+                for (int c = 0; c < D / 32; ++c) tc_ld32(o_addr + c * 32, ov[c]);
                 tc_wait_ld();
                 if (ti.n_kv == 0) {   // the tile saw no key: tensor memory holds nothing of ours, the rows are zeros
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
+                    for (int c = 0; c < D / 32; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) ov[c][i] = 0.0f;
                 }
                 unsigned char* stage = sm.q[t];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < D / 32; ++c) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 w;
@@ -871,17 +876,20 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (lane == 0) {
                     const int warp_row0 = (warp & 3) * 32;
                     tma_store_4d(&o_map, stage + warp_row0 * 128, 0, a.o_head0 + ti.head, sq.q_crow + ti.row0 + warp_row0, sq.q_cb);
-                    tma_store_4d(&o_map, stage + kHalfBytes + warp_row0 * 128, 64, a.o_head0 + ti.head, sq.q_crow + ti.row0 + warp_row0, sq.q_cb);
+                    if (D == 128)
+                        tma_store_4d(&o_map, stage + kHalfBytes + warp_row0 * 128, 64, a.o_head0 + ti.head, sq.q_crow + ti.row0 + warp_row0, sq.q_cb);
                     asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
                     asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // shared memory stays valid until read
                 }
             } else {
-                // Stage this warp's 32 rows (256 B each) in the Q tile's shared memory — every MMA that read
-                // Q_t has finished — so that the global stores are whole rows: 16 lanes x 16 B contiguous,
-                // two rows per instruction. That matters most for the peer copies, which cross NVLink.
+                // Stage this warp's 32 rows (2 D bytes each) in the Q tile's shared memory — every MMA that read
+                // Q_t has finished — so that the global stores are whole rows: D / 8 lanes x 16 B contiguous,
+                // 256 / D rows per instruction. That matters most for the peer copies, which cross NVLink.
+                constexpr int kRowBytes = D * 2;
+                constexpr int kChunks = D / 8;          // 16-byte chunks per row
                 unsigned char* stage = sm.q[t];
     #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < D / 32; ++c) {
                     float ov[32];
                     tc_ld32(o_addr + c * 32, ov);
                     tc_wait_ld();
@@ -897,21 +905,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         w.z = pack16<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv);
                         w.w = pack16<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv);
                         const int ch = c * 4 + i;   // 16-byte chunk of the row, XOR-swizzled against bank conflicts
-                        *reinterpret_cast<uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4)) = w;
+                        *reinterpret_cast<uint4*>(stage + r * kRowBytes + ((ch ^ (r & (kChunks - 1))) << 4)) = w;
                     }
                 }
                 __syncwarp();
                 {
-                    const int ch = lane & 15;
-                    const int sub = lane >> 4;
+                    const int ch = lane & (kChunks - 1);
+                    const int sub = lane / kChunks;
+                    constexpr int kRowsPerStep = 32 / kChunks;
                     const int warp_row0 = (warp & 3) * 32;
     #pragma unroll 4
-                    for (int it = 0; it < 16; ++it) {
-                        const int rr = warp_row0 + it * 2 + sub;
+                    for (int it = 0; it < 32 / kRowsPerStep; ++it) {
+                        const int rr = warp_row0 + it * kRowsPerStep + sub;
                         const int grow = ti.row0 + rr;
                         if (grow < sq.q_len) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * 256 + ((ch ^ (rr & 15)) << 4));
-                            const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * kD + ch * 8;
+                            const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * kRowBytes + ((ch ^ (rr & (kChunks - 1))) << 4));
+                            const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * D + ch * 8;
                             for (int pe = 0; pe < a.n_out; ++pe)
                                 *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
                         }
@@ -967,11 +976,11 @@ EncodeFn get_encode_fn() {
 }
 
 // (batch, seq, heads, 128) 16-bit tensor viewed as 4-D {d, head, seq, batch}; box = 64 x 1 x 128 x 1
-bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int box_rows = kBlockM) {
+bool encode_map(CUtensorMap* map, const void* base, int dtype, int d, int batch, int seq, int heads, int box_rows = kBlockM) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
-    const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2, (cuuint64_t)seq * heads * kD * 2};
+    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)seq * heads * d * 2};
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -984,11 +993,11 @@ bool encode_map(CUtensorMap* map, const void* base, int dtype, int batch, int se
 // box = 64 x 1 x block_size x 1: one page of one head and one 64-column half per copy. The C ABI
 // does not say how many blocks the pool has, so the block extent is set far beyond any pool; only
 // block ids read from the table are ever requested (and -1 for "no page": out of range, zeros).
-bool encode_paged_map(CUtensorMap* map, const void* base, int dtype, int block_size, int heads) {
+bool encode_paged_map(CUtensorMap* map, const void* base, int dtype, int d, int block_size, int heads) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)block_size, (cuuint64_t)1 << 30};
-    const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)heads * kD * 2, (cuuint64_t)block_size * heads * kD * 2};
+    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)block_size, (cuuint64_t)1 << 30};
+    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)block_size * heads * d * 2};
     if (strides[2] >= ((cuuint64_t)1 << 40)) return false;
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)block_size, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -1019,23 +1028,23 @@ int* status_word() {
     return g_status_word[dev];
 }
 
-template <typename T>
+template <typename T, int D>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
     CUtensorMap qm, km, vm, om;
     // packed varlen buffers are one "batch" of total rows
     const bool packed = p.mode == MODE_VARLEN;
     const int q_batch = packed ? 1 : p.num_seqs, q_rows = packed ? p.total_q : p.q_seq_len;
     const int k_batch = packed ? 1 : p.num_seqs, k_rows = packed ? p.total_k : p.kv_seq_len;
-    bool ok = encode_map(&qm, p.q, p.dtype, q_batch, q_rows, p.q_heads);
+    bool ok = encode_map(&qm, p.q, p.dtype, D, q_batch, q_rows, p.q_heads);
     // the output as 32-row boxes (one per softmax warp); only used when there is a single output buffer
-    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, q_batch, q_rows,
+    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, D, q_batch, q_rows,
                           p.n_out > 0 ? p.o_heads : p.q_heads, 32);
     if (p.paged) {
-        ok = ok && encode_paged_map(&km, p.k, p.dtype, p.block_size, p.kv_heads) &&
-             encode_paged_map(&vm, p.v, p.dtype, p.block_size, p.kv_heads);
+        ok = ok && encode_paged_map(&km, p.k, p.dtype, D, p.block_size, p.kv_heads) &&
+             encode_paged_map(&vm, p.v, p.dtype, D, p.block_size, p.kv_heads);
     } else {
-        ok = ok && encode_map(&km, p.k, p.dtype, k_batch, k_rows, p.kv_heads) &&
-             encode_map(&vm, p.v, p.dtype, k_batch, k_rows, p.kv_heads);
+        ok = ok && encode_map(&km, p.k, p.dtype, D, k_batch, k_rows, p.kv_heads) &&
+             encode_map(&vm, p.v, p.dtype, D, k_batch, k_rows, p.kv_heads);
     }
     if (!ok) return -1;  // let the SIMT kernel take it
     int* status = status_word();
@@ -1079,8 +1088,8 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     const int group = p.q_heads / p.kv_heads;
     const int num_mb = (p.q_seq_len + kBlockM - 1) / kBlockM;
     const int pairs = (group * num_mb + 1) / 2;
-    const size_t smem = sizeof(SharedStorage) + 1024;
-    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = sizeof(SharedStorage<D>) + 1024;
+    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) {
         set_last_errorf("prefill_tcgen05_kernel: %s", cudaGetErrorString(err));
         cudaGetLastError();
@@ -1100,7 +1109,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.band = band;
     if ((long long)p.kv_heads * p.num_seqs * band > 0x7fffffffLL) return -1;
     dim3 grid(p.kv_heads * p.num_seqs * band, (pairs + band - 1) / band);
-    prefill_tcgen05_kernel<T><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
+    prefill_tcgen05_kernel<T, D><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
     const int rc = check_launch("prefill_tcgen05_kernel");
     if (rc == FLASH_ATTN_OK) note_path("prefill_tcgen05", 1);
     return rc;
@@ -1147,7 +1156,7 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     }
     if (p.paged && (p.block_size < 8 || p.block_size > 128 || (128 % p.block_size) != 0)) return -1;
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
-    if (p.head_size != kD) return -1;
+    if (p.head_size != 64 && p.head_size != 128) return -1;
     if (!(p.scale > 0.0f)) return -1;
     if (p.q_seq_len < 16) return -1;   // a handful of rows is not worth a 128-row tile
     uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
@@ -1156,7 +1165,8 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     if (align & 15) return -1;
     const long long pairs = ((long long)(p.q_heads / p.kv_heads) * ((p.q_seq_len + kBlockM - 1) / kBlockM) + 1) / 2;
     if (pairs > 65535) return -1;
-    return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16>(p, stream) : launch_typed<__half>(p, stream);
+    if (p.head_size == 64) return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16, 64>(p, stream) : launch_typed<__half, 64>(p, stream);
+    return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16, 128>(p, stream) : launch_typed<__half, 128>(p, stream);
 }
 
 }  // namespace fa

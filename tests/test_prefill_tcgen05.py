@@ -92,3 +92,66 @@ def test_prefill_agrees_with_simt_kernel():
         ffi.set_option("force_generic", 0)
     torch.cuda.synchronize()
     assert (fast.float() - slow.float()).abs().max().item() <= 2e-2
+
+
+D64_SHAPES = [(1, 128, 128, 2, 2, 0), (2, 300, 300, 8, 2, 0), (1, 129, 200, 6, 6, 0), (2, 50, 120, 4, 4, 70),
+              (1, 640, 640, 3, 3, 0), (1, 1024, 1024, 4, 1, 128)]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", D64_SHAPES, ids=[str(s) for s in D64_SHAPES])
+def test_prefill_head_size_64(shape, dt):
+    """head_size 64 runs on the same kernel (one 64-column half per tile, N = 64 for P.V)."""
+    b, sq, skv, hq, hkv, sp = shape
+    d = 64
+    q = H.round_to(H.normal((b, sq, hq, d), 41 + sq), dt)
+    k = H.round_to(H.normal((b, skv, hkv, d), 42 + sq), dt)
+    v = H.round_to(H.normal((b, skv, hkv, d), 43 + sq), dt)
+    want, lse_want = ob.attn_f64_batch(q, k, v, start_pos=sp, return_lse=True)
+    qd, kd, vd = H.to_dev(q, dt), H.to_dev(k, dt), H.to_dev(v, dt)
+    o = torch.full_like(qd, float("nan"))
+    lse = torch.full((b, hq, sq), float("nan"), device="cuda", dtype=torch.float32)
+    low.flash_attn(qd, kd, vd, o, b, sq, skv, hq, hkv, d, sp, 1.0 / np.sqrt(d), None, None, lse)
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05"
+    assert ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o), want, f"prefill d=64 {shape} {dt}")
+    np.testing.assert_allclose(lse.cpu().numpy(), lse_want, rtol=0, atol=1e-3)
+
+
+def test_varlen_and_paged_head_size_64():
+    dt, d = "bf16", 64
+    ql, kl, hq, hkv = [100, 37, 260], [100, 37, 260], 4, 2
+    cu = np.concatenate([[0], np.cumsum(ql)]).astype(np.int32)
+    tq = int(cu[-1])
+    q = H.round_to(H.normal((tq, hq, d), 51), dt)
+    k = H.round_to(H.normal((tq, hkv, d), 52), dt)
+    v = H.round_to(H.normal((tq, hkv, d), 53), dt)
+    qd, kd, vd = H.to_dev(q, dt), H.to_dev(k, dt), H.to_dev(v, dt)
+    o = torch.full_like(qd, float("nan"))
+    c = torch.from_numpy(cu).cuda()
+    low.flash_attn_varlen(qd, kd, vd, o, c, c, len(ql), max(ql), max(kl), hq, hkv, d, 1.0 / np.sqrt(d))
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o), ob.attn_f64_varlen(q, k, v, cu, cu), "varlen d=64")
+
+    # chunked prefill over a paged cache, page size 16
+    bs, lens, sq = 16, np.array([300, 1000], dtype=np.int32), 64
+    need = (lens + bs - 1) // bs
+    rng = np.random.Generator(np.random.Philox(9))
+    nblocks = int(need.sum()) + 2
+    perm = rng.permutation(nblocks).astype(np.int32)
+    table = np.zeros((2, int(need.max()) + 1), dtype=np.int32)
+    pos = 0
+    for s_, n in enumerate(need):
+        table[s_, :n] = perm[pos:pos + n]
+        pos += int(n)
+    kc = H.round_to(H.normal((nblocks, bs, hkv, d), 54), dt)
+    vc = H.round_to(H.normal((nblocks, bs, hkv, d), 55), dt)
+    q2 = H.round_to(H.normal((2, sq, hq, d), 56), dt)
+    o2 = torch.full((2, sq, hq, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    low.flash_attn_with_kvcache(H.to_dev(q2, dt), H.to_dev(kc, dt), H.to_dev(vc, dt), o2, torch.from_numpy(table).cuda(),
+                                torch.from_numpy(lens).cuda(), 2, sq, hq, hkv, d, bs, table.shape[1], 1.0 / np.sqrt(d))
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o2), ob.attn_f64_kvcache(q2, kc, vc, lens, table), "paged prefill d=64")
