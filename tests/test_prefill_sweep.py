@@ -1,7 +1,7 @@
 """Seeded sweep of the tcgen05 prefill kernel against the f64 oracle over shapes drawn at random:
 batch, GQA widths, ragged and tile-aligned lengths, start positions that are and are not multiples
-of the tile (aligned diagonal tiles take a specialised softmax step), kv longer than needed, bf16
-and f16 — a guard against shape-dependent slips in the tile, band and mask arithmetic."""
+of the tile (aligned diagonal tiles take a specialised softmax step), kv longer than needed, head
+sizes 64 and 128, bf16 and f16 — a guard against shape-dependent slips in the tile, band and mask arithmetic."""
 import numpy as np
 import pytest
 import torch
@@ -26,7 +26,8 @@ def _cases(n, seed):
         extra = int(rng.choice([0, 0, int(rng.integers(1, 200))]))
         skv = sp + sq + extra if rng.random() < 0.8 else max(1, sp + sq - int(rng.integers(1, sq)))
         dt = "bf16" if i % 3 else "f16"
-        out.append((b, sq, skv, hkv * group, hkv, sp, dt))
+        d = 64 if i % 4 == 1 else 128
+        out.append((b, sq, skv, hkv * group, hkv, sp, dt, d))
     return out
 
 
@@ -35,8 +36,7 @@ CASES = _cases(36, 2024)
 
 @pytest.mark.parametrize("case", CASES, ids=[str(c) for c in CASES])
 def test_prefill_sweep(case):
-    b, sq, skv, hq, hkv, sp, dt = case
-    d = 128
+    b, sq, skv, hq, hkv, sp, dt, d = case
     q = H.round_to(H.normal((b, sq, hq, d), 101 + sq), dt)
     k = H.round_to(H.normal((b, skv, hkv, d), 102 + skv), dt)
     v = H.round_to(H.normal((b, skv, hkv, d), 103 + sq + skv), dt)
