@@ -81,8 +81,11 @@ def test_module_flash_matches_math_on_gpu(head_dim, seq, start_pos):
     assert path in ("prefill_tcgen05", "tile_simt")
     if head_dim in (64, 128) and start_pos == 0:
         assert path == "prefill_tcgen05"
+    # the attention outputs agree to the fused kernel's bar (max-abs 2e-2, mean-abs 2e-3 at unit scale);
+    # the output projection then rounds to bf16 at the magnitude of its results, so the bar scales with it
+    scale = max(1.0, ym.float().abs().max().item())
     err = (yf.float() - ym.float()).abs()
-    assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3
+    assert err.max().item() <= 2e-2 * scale and err.mean().item() <= 2e-3 * scale
     # with autograd on and parameters requiring grad, the Flash configuration refuses (no backward)
     with pytest.raises(F.FlashAttentionUnsupported):
         flash(x)
