@@ -289,7 +289,7 @@ def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, l
 
 def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d, steps, warmup, peaks, seed):
     """Packed variable-length prefill (the serving shape of the batched config): `num_seqs` prompts of
-    lo..hi tokens packed back to back, square causal per prompt, through flash_attn_varlen_bf16_total."""
+    lo..hi tokens packed back to back, square causal per prompt, through the reference's flash_attn_varlen_bf16 symbol."""
     rng = np.random.Generator(np.random.Philox(seed))
     lens = rng.integers(lo, hi + 1, size=num_seqs).astype(np.int64)
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
@@ -305,8 +305,7 @@ def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d,
     max_len = int(lens.max())
 
     def step():
-        low.flash_attn_varlen(q, k, v, o, cu_d, cu_d, num_seqs, max_len, max_len, hq, hkv, d, scale,
-                              total_q=total, total_k=total)
+        low.flash_attn_varlen(q, k, v, o, cu_d, cu_d, num_seqs, max_len, max_len, hq, hkv, d, scale)
 
     step()
     path, launches = ffi.last_path(), ffi.last_launches()

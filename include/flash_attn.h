@@ -103,9 +103,11 @@ int flash_attn_varlen_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* 
 
 /*
  * ADDITIVE (no counterpart in the reference): the packed entry point with the row counts of the
- * packed buffers, which lets f16/bf16 head_size-128 calls run on the tensor-core kernel (its bulk
- * copies need the buffers' extents; the reference signature above only has them on the device, in
- * cu_seqlens[num_seqs]). luma's high.rs knows both from the tensor shapes (high.rs:170-182).
+ * packed buffers. The reference signature above only has them on the device (cu_seqlens[num_seqs]);
+ * through it the tensor-core kernel's tensor maps carry no row bound and the tiles at the very end
+ * of the packed buffers are fetched with plain loads, never past the last row. With the counts the
+ * maps are bounded as well. Results are bit-identical. luma's high.rs knows both from the tensor
+ * shapes (high.rs:170-182).
  *   total_q : rows of q and o (= cu_seqlens_q[num_seqs])
  *   total_k : rows of contiguous k and v (= cu_seqlens_k[num_seqs]); ignored when k_paged != 0
  * Same checks, results and status codes as flash_attn_varlen_{f16,bf16}; totals <= 0 mean

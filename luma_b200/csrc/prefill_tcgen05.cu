@@ -2,8 +2,8 @@
 // tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
 // warp-specialised roles. Handles f16/bf16 storage with head_size 64 or 128 (template parameter D;
 // the layout comments below give the D = 128 figures), no padding mask, for the
-// batched entry point, chunked prefill over a paged cache, and the packed varlen entry point when
-// the caller gives the packed buffers' row counts. Replaces flash_attn_kernel
+// batched entry point, chunked prefill over a paged cache, and the packed varlen entry point (with
+// or without the packed buffers' row counts). Replaces flash_attn_kernel
 // (luma-flash-attn/kernels/flash_attn_func.cu:29-226), flash_attn_prefill_kernel
 // (kernels/flash_attn_with_kvcache.cu:157-277) and flash_attn_varlen_kernel
 // (kernels/flash_attn_varlen_func.cu:35-199), one-thread-per-query-row scalar kernels.
@@ -90,6 +90,9 @@ struct PrefillArgs {
     int band;       // tile pairs of one (batch, KV head) that sit next to each other in blockIdx.x
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
     int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
+    const void* q;              // MODE_VARLEN: the packed q / k / v buffers themselves, for the tiles at their very end
+    const void* k;
+    const void* v;
     const int* cu_q;            // MODE_VARLEN: packed row offsets of q / o
     const int* cu_k;            // MODE_VARLEN: packed row offsets (or, paged, lengths by difference) of k / v
     const int* context_lens;    // MODE_KVCACHE: cached length per sequence, query tokens included
@@ -403,6 +406,31 @@ __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExte
     }
 }
 
+// A 128-row tile of a packed (varlen) buffer that would reach past the buffer's last row, fetched by
+// one warp with plain loads: the reference's varlen signature does not say how many rows the packed
+// buffers hold, so their tensor maps carry no row bound, and a bulk copy must never be asked for
+// rows that may not exist. Rows past the end are written as zeros (what an out-of-range bulk copy
+// delivers). Same shared-memory image as the bulk copies: 64-column halves, 128 B per row, 16-byte
+// chunks XOR-swizzled by the row. The barrier's phase is completed by one plain arrival.
+template <int D>
+__device__ __forceinline__ void edge_tile_copy(unsigned char* dst, const void* base, int heads, int head, long long row_start,
+                                               long long total_rows, unsigned long long* bar, int lane) {
+    constexpr int kChunksPerRow = D / 8;   // 16-byte chunks per row
+    const long long left = total_rows - row_start;
+    const int nrows = left < 0 ? 0 : (left > kBlockN ? kBlockN : (int)left);
+    const unsigned char* src = static_cast<const unsigned char*>(base);
+#pragma unroll 4
+    for (int idx = lane; idx < kBlockN * kChunksPerRow; idx += 32) {
+        const int r = idx / kChunksPerRow, cc = idx % kChunksPerRow;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nrows) w = *reinterpret_cast<const uint4*>(src + ((row_start + r) * heads + head) * (long long)(D * 2) + cc * 16);
+        *reinterpret_cast<uint4*>(dst + (cc >> 3) * kHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4)) = w;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> tensor-core reads
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -436,6 +464,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     // and the K/V tiles that fill the empty ring), before the CTA-wide set-up barrier: the copies
     // then fly while tensor memory is being allocated and the other warps start up.
     const int n_pre = min(kStages, n_max);
+    // Packed buffers end at row cu_seqlens[num_seqs]; a tile that reaches past that row is not asked
+    // of the copy engine (see edge_tile_copy) but fetched by the producer warp after the set-up.
+    const bool packed = a.mode == MODE_VARLEN;
+    const long long tot_q = packed ? (long long)a.cu_q[a.batch] : 0;
+    const long long tot_k = (packed && !a.paged) ? (long long)a.cu_k[a.batch] : 0;
+    auto q_edge = [&](const TileInfo& ti) { return packed && ti.valid && (long long)sq.q_crow + ti.row0 + kBlockM > tot_q; };
+    auto kv_edge = [&](int j) { return packed && !a.paged && (long long)sq.kv_crow + (long long)(j + 1) * kBlockN > tot_k; };
     if (warp == kLoadWarp && lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&q_map) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&k_map) : "memory");
@@ -457,7 +492,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         auto load_q = [&](const TileInfo& ti, int t) {
-            if (!ti.valid) return;
+            if (!ti.valid || q_edge(ti)) return;
             mbar_expect_tx(&sm.q_full[t], TileBytes<D>::value);
             tma_load_4d(sm.q[t], &q_map, &sm.q_full[t], 0, ti.head, sq.q_crow + ti.row0, sq.q_cb);
             if (D == 128) tma_load_4d(sm.q[t] + kHalfBytes, &q_map, &sm.q_full[t], 64, ti.head, sq.q_crow + ti.row0, sq.q_cb);
@@ -466,9 +501,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             load_kv_tile<D>(a, sq, b, kvh, dst, map, bar, j);
         };
         load_q(t0, 0);
-        if (n_pre > 0) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
+        if (n_pre > 0 && !kv_edge(0)) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
         load_q(t1, 1);
-        for (int j = 1; j < n_pre; ++j) load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
+        for (int j = 1; j < n_pre; ++j)
+            if (!kv_edge(j)) load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
         // the V tiles come from a producer thread of their own (warp kLoadWarpV), after the set-up barrier
     }
     if (warp == kMmaWarp) {
@@ -500,35 +536,47 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         // One thread streams the K tiles (and loaded Q before), one the V tiles: with a paged cache a
         // tile is one copy per page and 64-column half plus a block-table read per page, and a single
         // thread issuing both rings cannot keep up with the tensor pipe at small page sizes.
-        if (lane == 0) {
+        // The warps run their loops whole; lane 0 issues the bulk copies, and all lanes share the
+        // plain-load copy of a tile at the very end of a packed buffer.
+        {
             const bool is_v = warp == kLoadWarpV;
             unsigned char (*ring)[TileBytes<D>::value] = is_v ? sm.v : sm.k;
             unsigned long long* full = is_v ? sm.v_full : sm.k_full;
             unsigned long long* empty = is_v ? sm.v_empty : sm.k_empty;
             const CUtensorMap* map = is_v ? &v_map : &k_map;
+            const void* kv_base = is_v ? a.v : a.k;
             bool alive = true;
+            if (!is_v) {   // what the set-up left out: Q tiles and first K tiles at the end of the packed buffers
+                if (q_edge(t0)) edge_tile_copy<D>(sm.q[0], a.q, a.q_heads, t0.head, (long long)sq.q_crow + t0.row0, tot_q, &sm.q_full[0], lane);
+                if (q_edge(t1)) edge_tile_copy<D>(sm.q[1], a.q, a.q_heads, t1.head, (long long)sq.q_crow + t1.row0, tot_q, &sm.q_full[1], lane);
+                for (int j = 0; j < n_pre; ++j)
+                    if (kv_edge(j)) edge_tile_copy<D>(sm.k[j], a.k, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &sm.k_full[j], lane);
+            }
             int issued = is_v ? 0 : n_pre;   // K tiles 0 .. n_pre-1 were issued during set-up
             for (int j = issued; j < n_max && alive; ++j) {
                 const int s = j % kStages;
                 if (j >= kStages) {
-                    alive = mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a.status, is_v ? 2 : 1);
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a.status, is_v ? 2 : 1));
                     if (!alive) break;
                 }
-                load_kv_tile<D>(a, sq, b, kvh, ring[s], map, &full[s], j);
+                if (kv_edge(j)) edge_tile_copy<D>(ring[s], kv_base, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &full[s], lane);
+                else if (lane == 0) load_kv_tile<D>(a, sq, b, kvh, ring[s], map, &full[s], j);
                 issued = j + 1;
             }
-            // Make sure none of this thread's bulk copies is still in flight when the CTA exits: wait
+            // Make sure none of this warp's copies is still in flight when the CTA exits: wait
             // (bounded) for the last fill of every stage (and of the Q tiles). These waits ignore the
             // abort flag: they only depend on the copy engine.
-            if (!is_v) {
-                if (t0.valid) mbar_wait(sm, &sm.q_full[0], 0, a.status, 3);
-                if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a.status, 3);
-            }
-            const unsigned long long t_begin = global_timer_ns();
-            for (int s = 0; s < kStages; ++s) {
-                if (issued <= s) continue;   // never filled
-                const int last = issued - 1 - (issued - 1 - s) % kStages;   // last issued tile of this stage
-                while (!mbar_try_wait(&full[s], (unsigned)(last / kStages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
+            if (lane == 0) {
+                if (!is_v) {
+                    if (t0.valid) mbar_wait(sm, &sm.q_full[0], 0, a.status, 3);
+                    if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a.status, 3);
+                }
+                const unsigned long long t_begin = global_timer_ns();
+                for (int s = 0; s < kStages; ++s) {
+                    if (issued <= s) continue;   // never filled
+                    const int last = issued - 1 - (issued - 1 - s) % kStages;   // last issued tile of this stage
+                    while (!mbar_try_wait(&full[s], (unsigned)(last / kStages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
+                }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -976,11 +1024,17 @@ EncodeFn get_encode_fn() {
 }
 
 // (batch, seq, heads, 128) 16-bit tensor viewed as 4-D {d, head, seq, batch}; box = 64 x 1 x 128 x 1
+// seq <= 0: a packed buffer whose row count the caller did not give (batch is 1 then). The row extent is
+// set beyond any buffer and the kernel never asks for a box that reaches past the real last row.
 bool encode_map(CUtensorMap* map, const void* base, int dtype, int d, int batch, int seq, int heads, int box_rows = kBlockM) {
     EncodeFn fn = get_encode_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)seq, (cuuint64_t)batch};
-    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)seq * heads * d * 2};
+    const bool unbounded = seq <= 0;
+    const cuuint64_t rows = unbounded ? (cuuint64_t)0x7fffffff : (cuuint64_t)seq;
+    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, rows, (cuuint64_t)batch};
+    // the stride of the batch axis is never used when batch is 1; it only has to be a legal value
+    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2,
+                                   unbounded ? (cuuint64_t)heads * d * 2 * 128 : (cuuint64_t)seq * heads * d * 2};
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -1076,6 +1130,9 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.kv_heads = p.kv_heads;
     a.start_pos = p.start_pos;
     a.mode = p.mode;
+    a.q = p.q;
+    a.k = p.k;
+    a.v = p.v;
     a.cu_q = p.cu_q;
     a.cu_k = p.cu_k;
     a.context_lens = p.context_lens;
@@ -1142,15 +1199,14 @@ int prefill_debug_read(void* dst, int bytes) {
 
 int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     // batched entry point, chunked prefill over a paged cache (whole pages must tile the 128-key
-    // K/V tile), and the packed varlen entry point when the caller said how many rows the packed
-    // buffers have (the reference signature does not: without them no tensor map with exact bounds
-    // can be built on the host, and the call stays on the SIMT kernel).
+    // K/V tile), and the packed varlen entry point. The reference's varlen signature does not say how
+    // many rows the packed buffers have: their tensor maps then carry no row bound, and the kernel
+    // fetches the tiles at the very end of the buffers with plain loads (edge_tile_copy).
     if (p.mask != nullptr) return -1;
     if (p.mode == MODE_KVCACHE) {
         if (!p.paged || p.max_blocks <= 0) return -1;
     } else if (p.mode == MODE_VARLEN) {
-        if (p.total_q <= 0) return -1;
-        if (p.paged ? p.max_blocks <= 0 : p.total_k <= 0) return -1;
+        if (p.paged && p.max_blocks <= 0) return -1;
     } else if (p.mode != MODE_BATCH) {
         return -1;
     }

@@ -98,17 +98,16 @@ def flash_attn_varlen(q, k, v, o, cu_seqlens_q, cu_seqlens_k, num_seqs, max_seql
                       stream=None, total_q=None, total_k=None) -> None:
     """Packed variable-length attention (low.rs:231-295). With `block_tables` the K/V are a paged
     cache and max_blocks is inferred as block_tables.numel() // num_seqs (low.rs:266-269).
-    For 16-bit storage the row counts of the packed buffers (by default taken from the buffers'
-    sizes) go along through the additive `flash_attn_varlen_<T>_total` entry point, which lets
-    head_size-128 calls run on the tensor-core kernel."""
+    The call goes through the reference's symbol. When the caller gives the row counts of the packed
+    buffers (`total_q`, and `total_k` unless paged) and the storage is 16-bit, they go along through
+    the additive `flash_attn_varlen_<T>_total` entry point and bound the tensor maps as well; the
+    results are bit-identical either way."""
     sfx = _suffix(q)
     k_paged = 1 if block_tables is not None else 0
     max_blocks = (block_tables.numel() // num_seqs) if (block_tables is not None and num_seqs > 0) else 0
-    if sfx in ("f16", "bf16") and q_heads > 0 and kv_heads > 0 and head_size > 0:
-        if total_q is None:
-            total_q = q.numel() // (q_heads * head_size)
+    if sfx in ("f16", "bf16") and total_q is not None and (k_paged or total_k is not None):
         if total_k is None:
-            total_k = 0 if k_paged else k.numel() // (kv_heads * head_size)
+            total_k = 0
         code = getattr(ffi.lib, f"flash_attn_varlen_{sfx}_total")(
             _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k),
             _ptr(block_tables), num_seqs, max_seqlen_q, max_seqlen_k, q_heads, kv_heads, head_size,

@@ -1,9 +1,10 @@
-"""Packed variable-length prefill on the tcgen05 kernel (the additive `_total` entry point) against
-the f64 oracle: ragged sequences whose tiles overhang into the next sequence's rows, a last
-sequence that ends inside a tile (the bulk copies must stop at the buffers' ends), prefixes
-(kv longer than q, bottom-right causal), sequences shorter than the grid's row range, GQA and MHA
-pairing, contiguous and paged K/V with permuted block tables; and that the reference signature
-(no totals) still gives the same numbers through the SIMT kernel."""
+"""Packed variable-length prefill on the tcgen05 kernel against the f64 oracle, through the reference
+signature (no row counts: the tiles at the very end of the packed buffers come in by plain loads)
+and through the additive `_total` entry point (row counts as tensor-map bounds): ragged sequences
+whose tiles overhang into the next sequence's rows, a last sequence that ends inside a tile (no
+copy may reach past the buffers' ends), prefixes (kv longer than q, bottom-right causal), sequences
+shorter than the grid's row range, GQA and MHA pairing, contiguous and paged K/V with permuted
+block tables."""
 import numpy as np
 import pytest
 import torch
@@ -44,20 +45,28 @@ def test_varlen_contiguous_matches_oracle(case, dt):
     cq = torch.from_numpy(cu_q).cuda()
     ck = torch.from_numpy(cu_k).cuda()
     o = torch.full_like(qd, float("nan"))
-    low.flash_attn_varlen(qd, kd, vd, o, cq, ck, len(ql), max(ql), max(kl), hq, hkv, D, 1.0 / np.sqrt(D))
+    low.flash_attn_varlen(qd, kd, vd, o, cq, ck, len(ql), max(ql), max(kl), hq, hkv, D, 1.0 / np.sqrt(D),
+                          total_q=tq, total_k=tk)      # the additive entry point: row counts bound the tensor maps
     torch.cuda.synchronize()
     assert ffi.last_path() == "prefill_tcgen05"
     assert ffi.device_status() == 0
     H.assert_bf16_close(H.to_np(o), want, f"varlen {case} {dt}")
 
-    # the reference signature carries no totals: same numbers from the SIMT kernel
+    # the reference signature carries no totals: same kernel, bit-identical output. The packed buffers
+    # are followed by rows of NaN here: whatever is read past the last row would poison the result.
+    def with_nan_tail(t):
+        buf = torch.full((t.shape[0] + 160,) + tuple(t.shape[1:]), float("nan"), device="cuda", dtype=t.dtype)
+        buf[:t.shape[0]] = t
+        return buf[:t.shape[0]]
+    qd, kd, vd = with_nan_tail(qd), with_nan_tail(kd), with_nan_tail(vd)
     o2 = torch.full_like(qd, float("nan"))
     sfx = "bf16" if dt == "bf16" else "f16"
     rc = getattr(ffi.lib, f"flash_attn_varlen_{sfx}")(
         qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o2.data_ptr(), cq.data_ptr(), ck.data_ptr(), None,
         len(ql), max(ql), max(kl), hq, hkv, D, 1, 0, 0, 1.0 / np.sqrt(D), None)
     torch.cuda.synchronize()
-    assert rc == 0 and ffi.last_path() == "tile_simt"
+    assert rc == 0 and ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    assert torch.equal(o2, o)
     H.assert_bf16_close(H.to_np(o2), want, f"varlen (reference signature) {case} {dt}")
 
 
@@ -90,6 +99,13 @@ def test_varlen_paged_matches_oracle(block_size):
     assert ffi.last_path() == "prefill_tcgen05"
     assert ffi.device_status() == 0
     H.assert_bf16_close(H.to_np(o), want, f"varlen paged bs={block_size}")
+    # with the row count of q given (the additive entry point): the same bits
+    o2 = torch.full_like(qd, float("nan"))
+    low.flash_attn_varlen(qd, kd, vd, o2, torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_k).cuda(), len(ql),
+                          max(ql), max(kl), hq, hkv, D, 1.0 / np.sqrt(D),
+                          block_tables=torch.from_numpy(table).cuda(), block_size=block_size, total_q=tq)
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and torch.equal(o2, o)
 
 
 def test_varlen_neighbouring_rows_are_not_touched():
