@@ -45,6 +45,30 @@ def test_paged_chunked_prefill_matches_oracle(sq, hq, hkv, bs, dt):
     H.assert_bf16_close(got, want, f"paged prefill sq={sq} {hq}/{hkv} bs={bs} {dt}")
 
 
+@pytest.mark.parametrize("sq", [2, 5, 15])
+def test_short_query_chunks_run_on_the_tensor_core_kernel(sq):
+    """A few query tokens per sequence over a long cache (speculative decoding, small prefill chunks):
+    every chunk longer than one token takes the tensor-core kernel, most rows of its tiles empty."""
+    lens = [sq, sq + 1, 700, 16, 1500 + sq, 129]
+    got, want, path = _run(lens, sq, 8, 2, 16, "bf16", seed=900 + sq)
+    assert path == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(got, want, f"paged prefill, {sq}-token chunks")
+
+
+@pytest.mark.parametrize("s,hq,hkv", [(2, 2, 2), (7, 8, 2), (15, 6, 3)])
+def test_short_sequences_batched_entry_point(s, hq, hkv):
+    d = 128
+    q = H.round_to(H.normal((3, s, hq, d), 70 + s), "bf16")
+    k = H.round_to(H.normal((3, s, hkv, d), 71 + s), "bf16")
+    v = H.round_to(H.normal((3, s, hkv, d), 72 + s), "bf16")
+    qd = H.to_dev(q, "bf16")
+    o = torch.full_like(qd, float("nan"))
+    low.flash_attn(qd, H.to_dev(k, "bf16"), H.to_dev(v, "bf16"), o, 3, s, s, hq, hkv, d, 0, 1.0 / np.sqrt(d))
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o), ob.attn_f64_batch(q, k, v, start_pos=0), f"batched, S={s}")
+
+
 def test_paged_prefill_short_and_empty_contexts():
     # contexts shorter than the chunk: rows that sit before the cache see nothing and output zeros
     # (flash_attn_with_kvcache.cu:185-195,270-275); an empty context outputs zeros everywhere
