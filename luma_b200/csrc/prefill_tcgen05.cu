@@ -1,8 +1,8 @@
 // Causal, GQA-capable flash-attention prefill forward for sm_100a: TMA-fed Q/K/V tiles,
 // tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
 // warp-specialised roles. Handles f16/bf16 storage with head_size 64 or 128 (template parameter D;
-// the layout comments below give the D = 128 figures), no padding mask, for the
-// batched entry point, chunked prefill over a paged cache, and the packed varlen entry point (with
+// the layout comments below give the D = 128 figures) for the batched entry point (optional
+// key-padding mask: template parameter kMask), chunked prefill over a paged cache, and the packed varlen entry point (with
 // or without the packed buffers' row counts). Replaces flash_attn_kernel
 // (luma-flash-attn/kernels/flash_attn_func.cu:29-226), flash_attn_prefill_kernel
 // (kernels/flash_attn_with_kvcache.cu:157-277) and flash_attn_varlen_kernel
@@ -93,6 +93,7 @@ struct PrefillArgs {
     const void* q;              // MODE_VARLEN: the packed q / k / v buffers themselves, for the tiles at their very end
     const void* k;
     const void* v;
+    const unsigned char* mask;  // MODE_BATCH: optional (batch, kv_seq_len) key-padding mask, 1 = valid key
     const int* cu_q;            // MODE_VARLEN: packed row offsets of q / o
     const int* cu_k;            // MODE_VARLEN: packed row offsets (or, paged, lengths by difference) of k / v
     const int* context_lens;    // MODE_KVCACHE: cached length per sequence, query tokens included
@@ -431,7 +432,9 @@ __device__ __forceinline__ void edge_tile_copy(unsigned char* dst, const void* b
     if (lane == 0) mbar_arrive(bar);
 }
 
-template <typename T, int D>
+// kMask: the call carries a key-padding mask (a separate instantiation, so that calls without one
+// pay nothing for it in the softmax loop)
+template <typename T, int D, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map, const PrefillArgs a) {
@@ -701,7 +704,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // 32 compares instead of 128, FMA-pipe exponentials in the full chunks, no work in the
             // unseen ones. Any other masked tile (cut by the end of K/V, unaligned start) takes the
             // general code below.
-            const bool diag_tile = need_mask && (long long)sq.pos_off + ti.row0 == (long long)key0 &&
+            // Key-padding mask (batched entry point): the tile's 128 validity bytes become four ballots;
+            // a tile whose keys are all valid — the usual case, padding sits at one end — runs as if
+            // there were no mask, any other takes the general step with the bits applied first.
+            unsigned kb0 = 0xffffffffu, kb1 = 0xffffffffu, kb2 = 0xffffffffu, kb3 = 0xffffffffu;
+            bool pad = false;
+            if (kMask) {
+                const unsigned char* mrow = a.mask + (long long)b * a.kv_seq_len;
+                const int kk = key0 + lane;
+                kb0 = __ballot_sync(0xffffffffu, kk < sq.kv_len && mrow[kk < sq.kv_len ? kk : 0] != 0);
+                kb1 = __ballot_sync(0xffffffffu, kk + 32 < sq.kv_len && mrow[kk + 32 < sq.kv_len ? kk + 32 : 0] != 0);
+                kb2 = __ballot_sync(0xffffffffu, kk + 64 < sq.kv_len && mrow[kk + 64 < sq.kv_len ? kk + 64 : 0] != 0);
+                kb3 = __ballot_sync(0xffffffffu, kk + 96 < sq.kv_len && mrow[kk + 96 < sq.kv_len ? kk + 96 : 0] != 0);
+                // keys past kv_len are cut by `limit` already; only padding among the real keys counts here
+                const int real = min(kBlockN, sq.kv_len - key0);
+                const unsigned w0 = real >= 32 ? 0xffffffffu : ((1u << max(real, 0)) - 1u);
+                const unsigned w1 = real >= 64 ? 0xffffffffu : (real <= 32 ? 0u : ((1u << (real - 32)) - 1u));
+                const unsigned w2 = real >= 96 ? 0xffffffffu : (real <= 64 ? 0u : ((1u << (real - 64)) - 1u));
+                const unsigned w3 = real >= 128 ? 0xffffffffu : (real <= 96 ? 0u : ((1u << (real - 96)) - 1u));
+                pad = ((kb0 & w0) != w0) || ((kb1 & w1) != w1) || ((kb2 & w2) != w2) || ((kb3 & w3) != w3);
+            }
+            const bool diag_tile = !(kMask && pad) && need_mask && (long long)sq.pos_off + ti.row0 == (long long)key0 &&
                                    (long long)sq.pos_off + ti.row0 + kBlockM - 1 <= (long long)sq.kv_len - 1;
             if (diag_tile) {
                 const int w = warp & 3;
@@ -796,6 +819,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sv[c]);
                 tc_wait_ld();
+                if (kMask && pad) {   // padded keys first: the bits are dead after this
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (!((kb0 >> i) & 1u)) sv[0][i] = -INFINITY;
+                        if (!((kb1 >> i) & 1u)) sv[1][i] = -INFINITY;
+                        if (!((kb2 >> i) & 1u)) sv[2][i] = -INFINITY;
+                        if (!((kb3 >> i) & 1u)) sv[3][i] = -INFINITY;
+                    }
+                }
                 if (need_mask) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -867,7 +899,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         if (c == 0) trace_event(trace, t, j, 2);
                     }
                 };
-                if (need_mask) exp_phase(std::false_type{});
+                if (need_mask || (kMask && pad)) exp_phase(std::false_type{});
                 else exp_phase(std::true_type{});
                 float sum_lo, sum_hi;
                 unpack2(sum2, sum_lo, sum_hi);
@@ -883,7 +915,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (alive && ti.valid) {
             tc_fence_after();
             const bool row_ok = row < sq.q_len;
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            // with a padding mask a query row at a padded (or out-of-range) position outputs zeros (flash_attn_func.cu:77-84)
+            bool q_ok = true;
+            if (kMask) q_ok = row_ok && pos >= 0 && pos < (long long)sq.kv_len && a.mask[(long long)b * a.kv_seq_len + pos] != 0;
+            const float inv = (l > 0.0f && q_ok) ? 1.0f / l : 0.0f;
             // a bulk store writes every row of its box that lies inside the tensor: in a packed buffer the
             // rows after this sequence belong to the next one, so a tile that overhangs the end of its
             // sequence takes the row-guarded path
@@ -977,7 +1012,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             if (row_ok && a.lse != nullptr) {
                 a.lse[((long long)b * a.q_heads + ti.head) * a.q_seq_len + row] =
-                    l > 0.0f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                    (l > 0.0f && q_ok) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
             }
             trace_event(trace, t, kTraceSteps - 1, 0);       // epilogue stores issued
         }
@@ -1082,7 +1117,7 @@ int* status_word() {
     return g_status_word[dev];
 }
 
-template <typename T, int D>
+template <typename T, int D, bool kMask>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
     CUtensorMap qm, km, vm, om;
     // packed varlen buffers are one "batch" of total rows
@@ -1133,6 +1168,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.q = p.q;
     a.k = p.k;
     a.v = p.v;
+    a.mask = p.mode == MODE_BATCH ? static_cast<const unsigned char*>(p.mask) : nullptr;
     a.cu_q = p.cu_q;
     a.cu_k = p.cu_k;
     a.context_lens = p.context_lens;
@@ -1146,7 +1182,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     const int num_mb = (p.q_seq_len + kBlockM - 1) / kBlockM;
     const int pairs = (group * num_mb + 1) / 2;
     const size_t smem = sizeof(SharedStorage<D>) + 1024;
-    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<T, D, kMask>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) {
         set_last_errorf("prefill_tcgen05_kernel: %s", cudaGetErrorString(err));
         cudaGetLastError();
@@ -1166,7 +1202,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.band = band;
     if ((long long)p.kv_heads * p.num_seqs * band > 0x7fffffffLL) return -1;
     dim3 grid(p.kv_heads * p.num_seqs * band, (pairs + band - 1) / band);
-    prefill_tcgen05_kernel<T, D><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
+    prefill_tcgen05_kernel<T, D, kMask><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);
     const int rc = check_launch("prefill_tcgen05_kernel");
     if (rc == FLASH_ATTN_OK) note_path("prefill_tcgen05", 1);
     return rc;
@@ -1202,7 +1238,7 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     // K/V tile), and the packed varlen entry point. The reference's varlen signature does not say how
     // many rows the packed buffers have: their tensor maps then carry no row bound, and the kernel
     // fetches the tiles at the very end of the buffers with plain loads (edge_tile_copy).
-    if (p.mask != nullptr) return -1;
+    if (p.mask != nullptr && p.mode != MODE_BATCH) return -1;
     if (p.mode == MODE_KVCACHE) {
         if (!p.paged || p.max_blocks <= 0) return -1;
     } else if (p.mode == MODE_VARLEN) {
@@ -1221,8 +1257,13 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     if (align & 15) return -1;
     const long long pairs = ((long long)(p.q_heads / p.kv_heads) * ((p.q_seq_len + kBlockM - 1) / kBlockM) + 1) / 2;
     if (pairs > 65535) return -1;
-    if (p.head_size == 64) return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16, 64>(p, stream) : launch_typed<__half, 64>(p, stream);
-    return p.dtype == DT_BF16 ? launch_typed<__nv_bfloat16, 128>(p, stream) : launch_typed<__half, 128>(p, stream);
+    const bool masked = p.mask != nullptr;
+    if (p.head_size == 64) {
+        if (p.dtype == DT_BF16) return masked ? launch_typed<__nv_bfloat16, 64, true>(p, stream) : launch_typed<__nv_bfloat16, 64, false>(p, stream);
+        return masked ? launch_typed<__half, 64, true>(p, stream) : launch_typed<__half, 64, false>(p, stream);
+    }
+    if (p.dtype == DT_BF16) return masked ? launch_typed<__nv_bfloat16, 128, true>(p, stream) : launch_typed<__nv_bfloat16, 128, false>(p, stream);
+    return masked ? launch_typed<__half, 128, true>(p, stream) : launch_typed<__half, 128, false>(p, stream);
 }
 
 }  // namespace fa

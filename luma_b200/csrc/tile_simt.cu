@@ -1,7 +1,8 @@
 // SIMT tile kernel: the catch-all implementation behind every entry point. It covers what the
-// tensor-core kernels do not specialise for — f32 storage, head sizes 32/64, padding masks,
-// packed variable-length batches, chunked prefill over a paged cache — with f32 arithmetic
-// throughout. Semantics per entry point follow
+// tensor-core kernels do not take — f32 storage, head size 32, single query rows outside the
+// kv-cache entry point, page sizes that do not divide 128, unaligned buffers — for every entry
+// point (batched with padding mask, packed variable-length, chunked prefill over a paged cache),
+// with f32 arithmetic throughout. Semantics per entry point follow
 //   luma-flash-attn/kernels/flash_attn_func.cu:29-226        (batched, start_pos, padding mask)
 //   luma-flash-attn/kernels/flash_attn_varlen_func.cu:35-199 (packed, bottom-right causal, paged)
 //   luma-flash-attn/kernels/flash_attn_with_kvcache.cu:157-277 (chunked prefill over pages)

@@ -155,3 +155,39 @@ def test_varlen_and_paged_head_size_64():
     torch.cuda.synchronize()
     assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
     H.assert_bf16_close(H.to_np(o2), ob.attn_f64_kvcache(q2, kc, vc, lens, table), "paged prefill d=64")
+
+
+@pytest.mark.parametrize("kind", ["right_padding", "left_padding", "random", "all_ones", "one_row_all_masked"])
+@pytest.mark.parametrize("shape", [(2, 300, 300, 4, 2, 128, 0), (3, 130, 515, 6, 2, 64, 385), (1, 1024, 1024, 2, 2, 128, 0)])
+def test_key_padding_mask_on_the_tensor_core_kernel(kind, shape):
+    """The (batch, kv_seq_len) padding mask of the batched entry point (flash_attn_func.cu:96-104,
+    1 = valid key): tiles whose keys are all valid run unmasked, mixed tiles apply the bits, rows left
+    without any visible key output zeros."""
+    b, sq, skv, hq, hkv, d, sp = shape
+    rng = np.random.Generator(np.random.Philox(sum(map(ord, kind)) + sq))
+    mask = np.ones((b, skv), dtype=np.uint8)
+    if kind == "right_padding":
+        for i in range(b):
+            mask[i, rng.integers(1, skv):] = 0
+    elif kind == "left_padding":
+        for i in range(b):
+            mask[i, :rng.integers(1, skv - 1)] = 0
+    elif kind == "random":
+        mask = (rng.random((b, skv)) > 0.3).astype(np.uint8)
+    elif kind == "one_row_all_masked":
+        mask[0, :] = 0
+    q = H.round_to(H.normal((b, sq, hq, d), 81), "bf16")
+    k = H.round_to(H.normal((b, skv, hkv, d), 82), "bf16")
+    v = H.round_to(H.normal((b, skv, hkv, d), 83), "bf16")
+    want = ob.attn_f64_batch(q, k, v, start_pos=sp, mask=mask)
+    qd = H.to_dev(q, "bf16")
+    o = torch.full_like(qd, float("nan"))
+    low.flash_attn(qd, H.to_dev(k, "bf16"), H.to_dev(v, "bf16"), o, b, sq, skv, hq, hkv, d, sp, 1.0 / np.sqrt(d),
+                   torch.from_numpy(mask).cuda())
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    got = H.to_np(o)
+    assert np.isfinite(got).all()
+    H.assert_bf16_close(got, want, f"padding mask {kind} {shape}")
+    if kind == "one_row_all_masked":
+        assert np.all(got[0] == 0.0)
