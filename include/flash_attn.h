@@ -192,7 +192,7 @@ int flash_attn_bf16_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, 
  *   stores (posted writes over NVLink for peers): no TMA towards peers, no multicast, no waiting
  *   on peers inside the kernel. The caller synchronises the group (a barrier after the launch)
  *   before anyone reads the gathered tensor. lse (optional) is local: (batch, q_num_heads, q_seq_len).
- * f16/bf16, head_size 64 or 128, q_seq_len >= 2, scale > 0, 16-byte aligned buffers; otherwise
+ * f16/bf16, head_size 64 or 128, scale > 0, 16-byte aligned buffers; otherwise
  * INVALID_HEAD_SIZE / INVALID_SHAPE with a message.
  */
 int flash_attn_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,

@@ -311,7 +311,7 @@ int allgather_impl(int dtype, const void* q, const void* k, const void* v, void*
     }
     const int rc = launch_prefill_tcgen05(p, reinterpret_cast<cudaStream_t>(stream));
     if (rc < 0) {
-        set_last_error("flash_attn_allgather: this shape is outside the fused tensor-core path (needs q_seq_len >= 2, "
+        set_last_error("flash_attn_allgather: this shape is outside the fused tensor-core path (needs f16/bf16, head_size 64 or 128, "
                        "scale > 0, 16-byte aligned buffers)");
         return FLASH_ATTN_ERR_INVALID_SHAPE;
     }

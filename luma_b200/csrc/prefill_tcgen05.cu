@@ -1250,7 +1250,8 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
     if (p.head_size != 64 && p.head_size != 128) return -1;
     if (!(p.scale > 0.0f)) return -1;
-    if (p.q_seq_len < 2) return -1;    // single rows: the split-K decode kernel (kv-cache entry point) or the SIMT kernel
+    // (single-token calls of the kv-cache entry point never get here: the dispatcher tries the split-K
+    // decode kernel first; single rows through the batched or packed entry points do)
     uintptr_t align = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) |
                       reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.o);
     for (int i = 0; i < p.n_out && i < 8; ++i) align |= reinterpret_cast<uintptr_t>(p.o_peers[i]);

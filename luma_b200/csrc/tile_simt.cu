@@ -1,6 +1,6 @@
 // SIMT tile kernel: the catch-all implementation behind every entry point. It covers what the
-// tensor-core kernels do not take — f32 storage, head size 32, single query rows outside the
-// kv-cache entry point, page sizes that do not divide 128, unaligned buffers — for every entry
+// tensor-core kernels do not take — f32 storage, head size 32, page sizes that do not divide 128,
+// unaligned buffers — for every entry
 // point (batched with padding mask, packed variable-length, chunked prefill over a paged cache),
 // with f32 arithmetic throughout. Semantics per entry point follow
 //   luma-flash-attn/kernels/flash_attn_func.cu:29-226        (batched, start_pos, padding mask)

@@ -129,3 +129,46 @@ def test_varlen_neighbouring_rows_are_not_touched():
     assert torch.all(o[tq:] == 7.0)
     want = ob.attn_f64_varlen(q, k, v, cu, cu)
     H.assert_bf16_close(H.to_np(o[:tq]), want, "varlen overhang")
+
+
+def test_single_token_sequences_through_the_packed_entry_point():
+    """A decode step written as a packed batch (every sequence one query token over a paged cache,
+    the form continuous-batching callers use): takes the tensor-core kernel."""
+    dt, block_size, hq, hkv = "bf16", 16, 8, 2
+    kl = [1, 17, 400, 129, 1000]
+    ql = [1] * len(kl)
+    cu_q, cu_k = _cu(ql), _cu(kl)
+    rng = np.random.Generator(np.random.Philox(9))
+    need = [(n + block_size - 1) // block_size for n in kl]
+    n_blocks = sum(need) + 2
+    perm = rng.permutation(n_blocks).astype(np.int32)
+    table = np.zeros((len(kl), max(need)), dtype=np.int32)
+    pos = 0
+    for s, n in enumerate(need):
+        table[s, :n] = perm[pos:pos + n]
+        pos += n
+    q = H.round_to(H.normal((len(kl), hq, D), 91), dt)
+    kc = H.round_to(H.normal((n_blocks, block_size, hkv, D), 92), dt)
+    vc = H.round_to(H.normal((n_blocks, block_size, hkv, D), 93), dt)
+    want = ob.attn_f64_varlen(q, kc, vc, cu_q, cu_k, block_table=table)
+    qd = H.to_dev(q, dt)
+    o = torch.full_like(qd, float("nan"))
+    low.flash_attn_varlen(qd, H.to_dev(kc, dt), H.to_dev(vc, dt), o, torch.from_numpy(cu_q).cuda(),
+                          torch.from_numpy(cu_k).cuda(), len(kl), 1, max(kl), hq, hkv, D, 1.0 / np.sqrt(D),
+                          block_tables=torch.from_numpy(table).cuda(), block_size=block_size)
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o), want, "single-token packed batch")
+
+
+def test_single_row_batched_entry_point_with_start_pos():
+    dt, b, skv, hq, hkv = "bf16", 3, 777, 8, 4
+    q = H.round_to(H.normal((b, 1, hq, D), 94), dt)
+    k = H.round_to(H.normal((b, skv, hkv, D), 95), dt)
+    v = H.round_to(H.normal((b, skv, hkv, D), 96), dt)
+    qd = H.to_dev(q, dt)
+    o = torch.full_like(qd, float("nan"))
+    low.flash_attn(qd, H.to_dev(k, dt), H.to_dev(v, dt), o, b, 1, skv, hq, hkv, D, skv - 1, 1.0 / np.sqrt(D))
+    torch.cuda.synchronize()
+    assert ffi.last_path() == "prefill_tcgen05" and ffi.device_status() == 0
+    H.assert_bf16_close(H.to_np(o), ob.attn_f64_batch(q, k, v, start_pos=skv - 1), "single row, batched")
