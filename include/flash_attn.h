@@ -190,10 +190,18 @@ int flash_attn_bf16_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, 
  *             Peer buffers must be mapped into this process (CUDA IPC or symmetric memory).
  *   The kernel stores its heads at head index q_head_offset of every buffer with ordinary 16-byte
  *   stores (posted writes over NVLink for peers): no TMA towards peers, no multicast, no waiting
- *   on peers inside the kernel. The caller synchronises the group (a barrier after the launch)
- *   before anyone reads the gathered tensor. lse (optional) is local: (batch, q_num_heads, q_seq_len).
- * f16/bf16, head_size 64 or 128, scale > 0, 16-byte aligned buffers; otherwise
- * INVALID_HEAD_SIZE / INVALID_SHAPE with a message.
+ *   on peers inside the kernel. Every GPU of the group starts its walk over the buffers one past its
+ *   own (its index is taken as q_head_offset / q_num_heads), so that the group never aims at one
+ *   GPU at a time. The caller synchronises the group (a barrier after the launch) before anyone reads
+ *   the gathered tensor. lse (optional) is local: (batch, q_num_heads, q_seq_len). No tensor map is
+ *   ever made over a peer's buffer.
+ * f16/bf16, head_size 64 or 128 (else INVALID_HEAD_SIZE), scale > 0, 16-byte aligned buffers
+ * (else INVALID_SHAPE), each with a message.
+ *
+ * The _lse forms gather the log-sum-exp the same way (the reference's all_gather along dim 1 of
+ * (batch, heads, seq)): lse_peers is a HOST array of n_peers device pointers to the FULL
+ * (batch, q_heads_total, q_seq_len) f32 tensor of every GPU; this call's heads are written at head
+ * index q_head_offset of each.
  */
 int flash_attn_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
                              void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
@@ -203,6 +211,34 @@ int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_
                               void* const* o_peers, int n_peers, int q_heads_total, int q_head_offset, float* lse,
                               int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
                               int head_size, int start_pos, float scale, void* stream);
+
+int flash_attn_f16_allgather_lse(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                 void* const* o_peers, float* const* lse_peers, int n_peers, int q_heads_total,
+                                 int q_head_offset, int batch, int q_seq_len, int kv_seq_len, int q_num_heads,
+                                 int kv_num_heads, int head_size, int start_pos, float scale, void* stream);
+int flash_attn_bf16_allgather_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                  void* const* o_peers, float* const* lse_peers, int n_peers, int q_heads_total,
+                                  int q_head_offset, int batch, int q_seq_len, int kv_seq_len, int q_num_heads,
+                                  int kv_num_heads, int head_size, int start_pos, float scale, void* stream);
+
+/*
+ * Head-sharded single-token paged decode (q_seq_len == 1) with the output all-gather fused into the
+ * split-K merge kernel: every merged row is stored straight into the (num_seqs, 1, q_heads_total,
+ * head_size) output of every GPU of the group at head index q_head_offset (plain stores, as above).
+ * No counterpart in the reference (attention, then luma-dist's all_gather, luma-dist/src/backends/
+ * nccl/backend.rs:167-180). q / caches / tables as flash_attn_with_kvcache_<T>; this rank's caches
+ * hold its KV heads only. f16/bf16, head_size 64 or 128, 16-byte aligned caches, else INVALID_SHAPE.
+ */
+int flash_attn_with_kvcache_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k_cache,
+                                          const flash_attn_f16_t* v_cache, void* const* o_peers, int n_peers,
+                                          int q_heads_total, int q_head_offset, const int* block_tables,
+                                          const int* context_lens, int num_seqs, int q_heads, int kv_heads, int head_size,
+                                          int block_size, int max_blocks, float scale, void* stream);
+int flash_attn_with_kvcache_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k_cache,
+                                           const flash_attn_bf16_t* v_cache, void* const* o_peers, int n_peers,
+                                           int q_heads_total, int q_head_offset, const int* block_tables,
+                                           const int* context_lens, int num_seqs, int q_heads, int kv_heads, int head_size,
+                                           int block_size, int max_blocks, float scale, void* stream);
 
 /*
  * KV-cache append: the step before every paged decode / chunked prefill. No counterpart in the
@@ -249,6 +285,13 @@ int flash_attn_debug_block_slots(const int* block_tables, const int* context_len
  *     is cut into as many splits as fit.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *   - That first call is also the moment the 16 MiB become real on that device: CUDA loads a
+ *     library's device code lazily by default, so the array is backed with memory when the first
+ *     kernel or symbol of its module is touched, not when the process starts. A caller that is
+ *     about to hand all free device memory to its own pool must therefore make one call here first
+ *     (one sequence of one token is enough), or run with CUDA_MODULE_LOADING=EAGER; if the array
+ *     cannot be backed any more, the first call fails with FLASH_ATTN_ERR_CUDA and a message that
+ *     says so. From the second call on nothing is allocated by anyone.
  *   - All calls on a device share the one array. Nothing in it has to start at zero (every slot
  *     that is read was written earlier in the same call), but two calls that overlap on the GPU —
  *     different streams, or different threads — race on it; serialise them.
@@ -269,27 +312,46 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *   flash_attn_last_launches  : number of kernels that call launched.
  *   flash_attn_set_option     : named integer knobs (returns 0 if the name is known):
  *       "force_generic"       1 = route everything through the SIMT tile kernel
- *       "prefill_trace"       1 = record the timeline read by flash_attn_debug_read;
+ *       "prefill_trace"       (builds with -DFA_TRACE only; ignored otherwise)
+ *                             1 = record the timeline read by flash_attn_debug_read;
  *                             2 = stage the epilogue's rows in shared memory even for one output;
  *                             3 = log {start ns, end ns, SM id} of up to 2048 CTAs from byte 16384
  *       "prefill_trace_y"     blockIdx.y of the CTA whose timeline is recorded (0 = heaviest)
  *       "prefill_band"        tile pairs of one K/V stream launched next to each other (0 = automatic)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
+ *       "prefill_wait_us"     bound of every wait inside the tcgen05 prefill kernel, microseconds
+ *                             (0 = the default of 2 s)
+ *       "prefill_test_skip_k" test hook: 1 + index of a K tile the kernel's producer never requests,
+ *                             so that the wait for it runs out and the kernel returns early with its
+ *                             status word set (0 = off). Only for testing the error path below.
+ *     The knobs are atomics: they may be set while other threads launch.
  */
 /*
+ * Bounded waits and how their expiry is reported. Every wait inside the tcgen05 prefill kernel is
+ * bounded; a CTA whose wait runs out stores the wait's code in a per-device status word (mapped
+ * host memory), drains its copies, frees its tensor memory and returns: the launch ends, its output
+ * is undefined. Launches are asynchronous, so the entry point that made the launch has returned
+ * FLASH_ATTN_OK long before. The NEXT attention entry point called for that device looks at the
+ * word first (a host read, no synchronisation): if it is set, that call clears it, launches
+ * nothing and returns FLASH_ATTN_ERR_CUDA with a message naming the wait code; the call after is
+ * clean again.
  *   flash_attn_device_status  : synchronises the current device, then reads and clears its status
- *                               word. 0 = healthy. Non-zero = a bounded wait inside the tcgen05
- *                               prefill kernel expired (the value names the wait) and the outputs
- *                               of that launch are undefined; -1 = no device / not readable.
+ *                               word. 0 = healthy, non-zero = the code of an expired wait,
+ *                               -1 = no device / not readable.
+ *   flash_attn_release_workspaces : releases (stream-ordered) every split-K workspace the decode
+ *                               path holds; returns how many there were. The library keeps at most
+ *                               32 of them (one per device and stream, least recently used first out).
  */
 const char* flash_attn_version(void);
 int flash_attn_device_status(void);
+int flash_attn_release_workspaces(void);
 /*
- *   flash_attn_debug_read     : copies up to `bytes` (max 65536) of the current device's debug
- *                               area to host memory: int status word at byte 0; from byte 256,
- *                               when the option "prefill_trace" is 1, clock64 stamps of one CTA of
- *                               the last tcgen05 prefill launch, laid out [role 0..2][kv step
- *                               0..59][event 0..7] as int64. Returns bytes copied or -1.
+ *   flash_attn_debug_read     : builds with -DFA_TRACE only (returns -1 otherwise): copies up to
+ *                               `bytes` (max 65536) of the current device's debug area to host
+ *                               memory: int status word at byte 0; from byte 256, when the option
+ *                               "prefill_trace" is 1, clock64 stamps of one CTA of the last tcgen05
+ *                               prefill launch, laid out [role 0..2][kv step 0..59][event 0..7] as
+ *                               int64. Returns bytes copied or -1.
  */
 int flash_attn_debug_read(void* dst, int bytes);
 const char* flash_attn_last_path(void);

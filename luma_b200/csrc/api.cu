@@ -6,10 +6,11 @@
 //   luma-flash-attn/kernels/flash_attn_func.cu:267-304
 //   luma-flash-attn/kernels/flash_attn_varlen_func.cu:243-304
 //   luma-flash-attn/kernels/flash_attn_with_kvcache.cu:313-386
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
-#include <map>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -19,11 +20,14 @@ namespace {
 thread_local char g_last_error[256] = {0};
 thread_local const char* g_last_path = "";
 thread_local int g_last_launches = 0;
-int g_force_generic = 0;
-int g_decode_chunk = 0;
-int g_prefill_trace = 0;
-int g_prefill_trace_y = 0;
-int g_prefill_band = 0;
+// Option knobs: written by flash_attn_set_option on any thread, read by launches on any thread.
+std::atomic<int> g_force_generic{0};
+std::atomic<int> g_decode_chunk{0};
+std::atomic<int> g_prefill_trace{0};
+std::atomic<int> g_prefill_trace_y{0};
+std::atomic<int> g_prefill_band{0};
+std::atomic<int> g_prefill_wait_us{0};
+std::atomic<int> g_prefill_test_skip_k{0};
 }  // namespace
 
 void set_last_error(const char* msg) { std::snprintf(g_last_error, sizeof(g_last_error), "%s", msg); }
@@ -40,11 +44,13 @@ void note_path(const char* name, int launches) {
     g_last_launches = launches;
 }
 
-int get_option_force_generic() { return g_force_generic; }
-int get_option_decode_chunk() { return g_decode_chunk; }
-int get_option_prefill_trace() { return g_prefill_trace; }
-int get_option_prefill_trace_y() { return g_prefill_trace_y; }
-int get_option_prefill_band() { return g_prefill_band; }
+int get_option_force_generic() { return g_force_generic.load(std::memory_order_relaxed); }
+int get_option_decode_chunk() { return g_decode_chunk.load(std::memory_order_relaxed); }
+int get_option_prefill_trace() { return g_prefill_trace.load(std::memory_order_relaxed); }
+int get_option_prefill_trace_y() { return g_prefill_trace_y.load(std::memory_order_relaxed); }
+int get_option_prefill_band() { return g_prefill_band.load(std::memory_order_relaxed); }
+int get_option_prefill_wait_us() { return g_prefill_wait_us.load(std::memory_order_relaxed); }
+int get_option_prefill_test_skip_k() { return g_prefill_test_skip_k.load(std::memory_order_relaxed); }
 
 int check_launch(const char* what) {
     const cudaError_t err = cudaGetLastError();
@@ -56,41 +62,89 @@ int check_launch(const char* what) {
 }
 
 // ---- decode split-K workspace: one buffer per (device, stream) ---------------------------
+// Allocation and release are stream-ordered (cudaMallocAsync / cudaFreeAsync on the stream that
+// uses the buffer): growing a workspace neither takes a device-wide synchronisation nor frees
+// memory under work that still reads it. The table is bounded: beyond kMaxWorkspaces entries the
+// least recently used one is released, so a program that keeps creating streams does not keep
+// one buffer per stream it ever had (a stream handle that is destroyed and handed out again simply
+// finds a scratch buffer that nobody else uses).
 namespace {
 struct WsEntry {
+    int dev = -1;
+    cudaStream_t stream = nullptr;
     void* ptr = nullptr;
     size_t bytes = 0;
+    unsigned long long last_use = 0;
 };
+constexpr size_t kMaxWorkspaces = 32;
 std::mutex g_ws_mutex;
-std::map<std::pair<int, cudaStream_t>, WsEntry> g_ws;
+std::vector<WsEntry> g_ws;
+unsigned long long g_ws_clock = 0;
+
+void release_entry(WsEntry& e) {
+    if (e.ptr == nullptr) return;
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != e.dev) cudaSetDevice(e.dev);
+    if (cudaFreeAsync(e.ptr, e.stream) != cudaSuccess) {
+        cudaGetLastError();   // e.g. the stream is gone: fall back to the synchronising release
+        cudaFree(e.ptr);
+        cudaGetLastError();
+    }
+    if (cur != e.dev && cur >= 0) cudaSetDevice(cur);
+    e.ptr = nullptr;
+    e.bytes = 0;
+}
 }  // namespace
 
 void* decode_workspace(cudaStream_t stream, size_t bytes) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
     std::lock_guard<std::mutex> lock(g_ws_mutex);
-    WsEntry& e = g_ws[{dev, stream}];
-    if (e.bytes >= bytes && e.ptr != nullptr) return e.ptr;
-    if (e.ptr != nullptr) {
-        // cudaFree waits for work that may still read the old buffer
-        cudaFree(e.ptr);
-        e.ptr = nullptr;
-        e.bytes = 0;
+    WsEntry* e = nullptr;
+    for (WsEntry& w : g_ws)
+        if (w.dev == dev && w.stream == stream) e = &w;
+    if (e == nullptr) {
+        if (g_ws.size() >= kMaxWorkspaces) {
+            size_t lru = 0;
+            for (size_t i = 1; i < g_ws.size(); ++i)
+                if (g_ws[i].last_use < g_ws[lru].last_use) lru = i;
+            release_entry(g_ws[lru]);
+            g_ws.erase(g_ws.begin() + (long)lru);
+        }
+        g_ws.emplace_back();
+        e = &g_ws.back();
+        e->dev = dev;
+        e->stream = stream;
     }
+    e->last_use = ++g_ws_clock;
+    if (e->bytes >= bytes && e->ptr != nullptr) return e->ptr;
+    release_entry(*e);   // ordered after the work that still reads the old buffer
     size_t want = bytes + bytes / 4;
     if (want < (size_t(1) << 20)) want = size_t(1) << 20;
     void* ptr = nullptr;
-    if (cudaMalloc(&ptr, want) != cudaSuccess) {
+    if (cudaMallocAsync(&ptr, want, stream) != cudaSuccess) {
         cudaGetLastError();
         want = bytes;
-        if (cudaMalloc(&ptr, want) != cudaSuccess) {
+        if (cudaMallocAsync(&ptr, want, stream) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
     }
-    e.ptr = ptr;
-    e.bytes = want;
+    e->ptr = ptr;
+    e->bytes = want;
     return ptr;
+}
+
+int release_workspaces() {
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    int n = 0;
+    for (WsEntry& w : g_ws) {
+        if (w.ptr != nullptr) ++n;
+        release_entry(w);
+    }
+    g_ws.clear();
+    return n;
 }
 
 namespace {
@@ -131,6 +185,18 @@ bool have_device() {
     return true;
 }
 
+// A bounded wait of an earlier tensor-core prefill launch on the current device ran out: that launch
+// returned early and its output is undefined. The kernel left the wait's code in a host-mapped
+// word; it is reported here — without touching the device — as the failure of the next call, which
+// is the first moment the asynchronous ABI can say so (error contract: luma-flash-attn/src/error.rs:38-51).
+bool report_earlier_wait_expiry() {
+    const int code = prefill_take_status();
+    if (code == 0) return true;
+    set_last_errorf("flash_attn: a bounded wait (code %d) inside an earlier prefill_tcgen05 launch on this device ran out; "
+                    "that launch's output is undefined. This call did not run.", code);
+    return false;
+}
+
 int dispatch(const AttnParams& p, cudaStream_t stream) {
     if (!have_device()) return FLASH_ATTN_ERR_CUDA;
     DeviceGuard guard(p.q);
@@ -138,7 +204,8 @@ int dispatch(const AttnParams& p, cudaStream_t stream) {
         set_last_error("flash_attn: could not select the device that owns q");
         return FLASH_ATTN_ERR_CUDA;
     }
-    if (!g_force_generic) {
+    if (!report_earlier_wait_expiry()) return FLASH_ATTN_ERR_CUDA;
+    if (!get_option_force_generic()) {
         int rc = launch_decode_splitk(p, stream);
         if (rc >= 0) return rc;
         rc = launch_prefill_tcgen05(p, stream);
@@ -249,7 +316,8 @@ int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
 // kernel. Only the tcgen05 path implements it.
 int allgather_impl(int dtype, const void* q, const void* k, const void* v, void* const* o_peers, int n_peers,
                    int q_heads_total, int q_head_offset, float* lse, int batch, int q_seq_len, int kv_seq_len,
-                   int q_num_heads, int kv_num_heads, int head_size, int start_pos, float scale, void* stream) {
+                   int q_num_heads, int kv_num_heads, int head_size, int start_pos, float scale, void* stream,
+                   float* const* lse_peers = nullptr) {
     g_last_error[0] = '\0';
     cudaGetLastError();
     if (q == nullptr || k == nullptr || v == nullptr || o_peers == nullptr) {
@@ -282,9 +350,17 @@ int allgather_impl(int dtype, const void* q, const void* k, const void* v, void*
         set_last_error("flash_attn_allgather: start_pos must be >= 0");
         return FLASH_ATTN_ERR_INVALID_START_POS;
     }
-    if (head_size != 128) {
-        set_last_error("flash_attn_allgather: only head_size 128 is implemented on the fused path");
+    if (head_size != 64 && head_size != 128) {
+        set_last_error("flash_attn_allgather: the fused path takes head_size 64 or 128");
         return FLASH_ATTN_ERR_INVALID_HEAD_SIZE;
+    }
+    if (lse_peers != nullptr) {
+        for (int i = 0; i < n_peers; ++i) {
+            if (lse_peers[i] == nullptr) {
+                set_last_error("flash_attn_allgather: every entry of lse_peers must be a device pointer");
+                return FLASH_ATTN_ERR_NULL_PTR;
+            }
+        }
     }
     AttnParams p{};
     p.q = q; p.k = k; p.v = v; p.o = o_peers[0]; p.lse = lse;
@@ -303,12 +379,17 @@ int allgather_impl(int dtype, const void* q, const void* k, const void* v, void*
     p.n_out = n_peers;
     p.o_heads = q_heads_total;
     p.o_head0 = q_head_offset;
+    if (lse_peers != nullptr) {
+        for (int i = 0; i < n_peers; ++i) p.lse_peers[i] = lse_peers[i];
+        p.n_lse = n_peers;
+    }
     if (!have_device()) return FLASH_ATTN_ERR_CUDA;
     DeviceGuard guard(q);
     if (!guard.ok) {
         set_last_error("flash_attn_allgather: could not select the device that owns q");
         return FLASH_ATTN_ERR_CUDA;
     }
+    if (!report_earlier_wait_expiry()) return FLASH_ATTN_ERR_CUDA;
     const int rc = launch_prefill_tcgen05(p, reinterpret_cast<cudaStream_t>(stream));
     if (rc < 0) {
         set_last_error("flash_attn_allgather: this shape is outside the fused tensor-core path (needs f16/bf16, head_size 64 or 128, "
@@ -321,10 +402,11 @@ int allgather_impl(int dtype, const void* q, const void* k, const void* v, void*
 int kvcache_impl(int dtype, const void* q, const void* k_cache, const void* v_cache, void* o,
                  const int* block_tables, const int* context_lens, int num_seqs, int q_seq_len,
                  int q_heads, int kv_heads, int head_size, int block_size, int max_blocks,
-                 float scale, void* stream) {
+                 float scale, void* stream, void* const* o_peers = nullptr, int n_peers = 0,
+                 int q_heads_total = 0, int q_head_offset = 0) {
     g_last_error[0] = '\0';
     cudaGetLastError();
-    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || o == nullptr ||
+    if (q == nullptr || k_cache == nullptr || v_cache == nullptr || (o == nullptr && o_peers == nullptr) ||
         block_tables == nullptr || context_lens == nullptr) {
         set_last_error("flash_attn_with_kvcache: null pointer argument");
         return FLASH_ATTN_ERR_NULL_PTR;
@@ -366,6 +448,36 @@ int kvcache_impl(int dtype, const void* q, const void* k_cache, const void* v_ca
     p.max_blocks = max_blocks;
     p.paged = 1;
     p.scale = scale;
+    if (o_peers != nullptr) {
+        // head-sharded single-token decode with the output all-gather fused into the merge kernel
+        if (n_peers < 1 || n_peers > 8 || q_head_offset < 0 || q_heads_total <= 0 || q_head_offset + q_heads > q_heads_total) {
+            set_last_error("flash_attn_with_kvcache_allgather: n_peers must be in 1..8 and q_head_offset + q_heads inside q_heads_total");
+            return FLASH_ATTN_ERR_INVALID_SHAPE;
+        }
+        for (int i = 0; i < n_peers; ++i) {
+            if (o_peers[i] == nullptr) {
+                set_last_error("flash_attn_with_kvcache_allgather: every entry of o_peers must be a device pointer");
+                return FLASH_ATTN_ERR_NULL_PTR;
+            }
+            p.o_peers[i] = o_peers[i];
+        }
+        p.n_out = n_peers;
+        p.o_heads = q_heads_total;
+        p.o_head0 = q_head_offset;
+        if (!have_device()) return FLASH_ATTN_ERR_CUDA;
+        DeviceGuard guard(q);
+        if (!guard.ok) {
+            set_last_error("flash_attn_with_kvcache_allgather: could not select the device that owns q");
+            return FLASH_ATTN_ERR_CUDA;
+        }
+        const int rc = launch_decode_splitk(p, reinterpret_cast<cudaStream_t>(stream));
+        if (rc < 0) {
+            set_last_error("flash_attn_with_kvcache_allgather: outside the split-K decode path (needs q_seq_len 1, f16/bf16, "
+                           "head_size 64 or 128, 16-byte aligned caches)");
+            return FLASH_ATTN_ERR_INVALID_SHAPE;
+        }
+        return rc;
+    }
     return dispatch(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -389,6 +501,8 @@ int flash_attn_debug_read(void* dst, int bytes) {
     return fa::prefill_debug_read(dst, bytes);
 }
 
+int flash_attn_release_workspaces(void) { return fa::release_workspaces(); }
+
 int flash_attn_set_option(const char* name, int value) {
     if (name == nullptr) return 1;
     if (std::strcmp(name, "force_generic") == 0) {
@@ -409,6 +523,14 @@ int flash_attn_set_option(const char* name, int value) {
     }
     if (std::strcmp(name, "decode_chunk_tokens") == 0) {
         fa::g_decode_chunk = value;
+        return 0;
+    }
+    if (std::strcmp(name, "prefill_wait_us") == 0) {
+        fa::g_prefill_wait_us = value;
+        return 0;
+    }
+    if (std::strcmp(name, "prefill_test_skip_k") == 0) {
+        fa::g_prefill_test_skip_k = value;
         return 0;
     }
     return 1;
@@ -495,6 +617,48 @@ int flash_attn_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_
                               int start_pos, float scale, void* stream) {
     return fa::allgather_impl(fa::DT_BF16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, lse, batch, q_seq_len,
                               kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream);
+}
+
+int flash_attn_f16_allgather_lse(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                 void* const* o_peers, float* const* lse_peers, int n_peers, int q_heads_total,
+                                 int q_head_offset, int batch, int q_seq_len, int kv_seq_len, int q_num_heads,
+                                 int kv_num_heads, int head_size, int start_pos, float scale, void* stream) {
+    return fa::allgather_impl(fa::DT_F16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, nullptr, batch, q_seq_len,
+                              kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream, lse_peers);
+}
+int flash_attn_bf16_allgather_lse(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                  void* const* o_peers, float* const* lse_peers, int n_peers, int q_heads_total,
+                                  int q_head_offset, int batch, int q_seq_len, int kv_seq_len, int q_num_heads,
+                                  int kv_num_heads, int head_size, int start_pos, float scale, void* stream) {
+    return fa::allgather_impl(fa::DT_BF16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, nullptr, batch, q_seq_len,
+                              kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream, lse_peers);
+}
+
+int flash_attn_with_kvcache_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k_cache,
+                                          const flash_attn_f16_t* v_cache, void* const* o_peers, int n_peers,
+                                          int q_heads_total, int q_head_offset, const int* block_tables,
+                                          const int* context_lens, int num_seqs, int q_heads, int kv_heads, int head_size,
+                                          int block_size, int max_blocks, float scale, void* stream) {
+    if (o_peers == nullptr) {
+        fa::set_last_error("flash_attn_with_kvcache_allgather: o_peers must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    return fa::kvcache_impl(fa::DT_F16, q, k_cache, v_cache, nullptr, block_tables, context_lens, num_seqs, 1, q_heads,
+                            kv_heads, head_size, block_size, max_blocks, scale, stream, o_peers, n_peers, q_heads_total,
+                            q_head_offset);
+}
+int flash_attn_with_kvcache_bf16_allgather(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k_cache,
+                                           const flash_attn_bf16_t* v_cache, void* const* o_peers, int n_peers,
+                                           int q_heads_total, int q_head_offset, const int* block_tables,
+                                           const int* context_lens, int num_seqs, int q_heads, int kv_heads, int head_size,
+                                           int block_size, int max_blocks, float scale, void* stream) {
+    if (o_peers == nullptr) {
+        fa::set_last_error("flash_attn_with_kvcache_allgather: o_peers must not be null");
+        return FLASH_ATTN_ERR_NULL_PTR;
+    }
+    return fa::kvcache_impl(fa::DT_BF16, q, k_cache, v_cache, nullptr, block_tables, context_lens, num_seqs, 1, q_heads,
+                            kv_heads, head_size, block_size, max_blocks, scale, stream, o_peers, n_peers, q_heads_total,
+                            q_head_offset);
 }
 
 int flash_attn_kvcache_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,

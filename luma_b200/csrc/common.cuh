@@ -56,6 +56,9 @@ struct AttnParams {
     int n_out;
     int o_heads;
     int o_head0;
+    // the same for the log-sum-exp: n_lse > 0 buffers of (batch, o_heads, q_seq_len) f32
+    float* lse_peers[8];
+    int n_lse;
 };
 
 // Per-sequence extents. Query row i of the sequence sits at global position pos_off + i and
@@ -125,6 +128,8 @@ int get_option_decode_chunk();
 int get_option_prefill_trace();
 int get_option_prefill_trace_y();
 int get_option_prefill_band();
+int get_option_prefill_wait_us();       // bound of the tcgen05 kernel's waits in microseconds (0 = the default, 2 s)
+int get_option_prefill_test_skip_k();   // test hook: 1 + index of a K tile the producer never requests (0 = off)
 
 // Returns FLASH_ATTN_OK or FLASH_ATTN_ERR_CUDA (with last error set) after a launch.
 int check_launch(const char* what);
@@ -142,8 +147,10 @@ int launch_kv_append(int elem_bytes, const void* k_new, const void* v_new, void*
                      const int* block_tables, const int* context_lens, int num_seqs, int n_new, int kv_heads,
                      int head_size, int block_size, int max_blocks, cudaStream_t stream);
 
-// Reads and clears the per-device status word of the tcgen05 kernel (0 = every bounded wait was
-// satisfied; otherwise the code of the wait that expired). Synchronises the device.
+// Reads and clears the current device's status word of the tcgen05 kernel (0 = every bounded wait
+// was satisfied; otherwise the code of a wait that expired). The word is in mapped host memory:
+// prefill_take_status() only looks at it, prefill_device_status() synchronises the device first.
+int prefill_take_status();
 int prefill_device_status();
 // Copies the per-device debug area (status word, then from byte 256 the optional kernel timeline)
 // to host memory; returns the bytes copied or -1.
@@ -151,5 +158,7 @@ int prefill_debug_read(void* dst, int bytes);
 
 // Split-K scratch of the decode path: one buffer per (device, stream), grown on demand.
 void* decode_workspace(cudaStream_t stream, size_t bytes);
+// Releases every workspace (stream-ordered); returns how many buffers were held.
+int release_workspaces();
 
 }  // namespace fa

@@ -363,12 +363,20 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
     }
 }
 
+// Where the merged rows go: one buffer of (num_seqs, 1, o_heads, D), or — head-sharded decode with
+// the output all-gather fused in — the same tensor on every GPU of the group (peer memory, plain
+// stores over NVLink), each receiving this call's heads at head offset o_head0.
+struct MergeOut {
+    void* o[8];
+    int n_out, o_heads, o_head0, peer0;
+};
+
 // Merges the split-K partials of one (sequence, query head) and writes the output row.
 template <typename T, int D>
 __global__ void __launch_bounds__(D) decode_merge_kernel(const float* __restrict__ ws_acc,
                                                          const float2* __restrict__ ws_ml,
                                                          const int* __restrict__ context_lens,
-                                                         T* __restrict__ o, int q_heads, int chunk,
+                                                         const MergeOut out, int q_heads, int chunk,
                                                          int max_splits) {
     const int h = blockIdx.x;
     const int s = blockIdx.y;
@@ -387,7 +395,21 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float* __restrict
     }
     // reference: inv = l > 0 ? 1/l : 0 (flash_attn_with_kvcache.cu:109)
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    o[((long long)s * q_heads + h) * D + d] = from_f32<T>(acc * inv);
+    const T val = from_f32<T>(acc * inv);
+    const long long off = ((long long)s * out.o_heads + out.o_head0 + h) * D + d;
+    int pe = out.peer0;
+    for (int n = 0; n < out.n_out; ++n) {
+        static_cast<T*>(out.o[pe])[off] = val;
+        pe = pe + 1 == out.n_out ? 0 : pe + 1;
+    }
+}
+
+MergeOut merge_out_single(void* o, int q_heads) {
+    MergeOut m{};
+    m.o[0] = o;
+    m.n_out = 1;
+    m.o_heads = q_heads;
+    return m;
 }
 
 // Tokens per work item. A CTA needs several microseconds to fill its copy pipeline, so long
@@ -457,8 +479,15 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     int rc = check_launch("decode_splitk_kernel");
     if (rc != FLASH_ATTN_OK) return rc;
     dim3 mgrid(p.q_heads, p.num_seqs);
-    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, p.context_lens,
-                                                      static_cast<T*>(p.o), p.q_heads, chunk, max_splits);
+    MergeOut mo = merge_out_single(p.o, p.q_heads);
+    if (p.n_out > 0) {
+        for (int i = 0; i < p.n_out && i < 8; ++i) mo.o[i] = p.o_peers[i];
+        mo.n_out = p.n_out;
+        mo.o_heads = p.o_heads;
+        mo.o_head0 = p.o_head0;
+        mo.peer0 = (p.o_head0 / p.q_heads + 1) % p.n_out;
+    }
+    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, p.context_lens, mo, p.q_heads, chunk, max_splits);
     rc = check_launch("decode_merge_kernel");
     if (rc == FLASH_ATTN_OK) note_path("decode_splitk", 2);
     return rc;
@@ -491,7 +520,11 @@ int launch_decode_splitk(const AttnParams& p, cudaStream_t stream) {
 // a latency-critical step cannot afford cudaMalloc / cudaFree, which take the driver's allocation
 // lock and synchronise the whole device. For them the scratch is paid for once, when the library
 // is loaded: every GPU whose context loads libflash_attn holds kStaticScratchBytes of it until
-// the process exits, whether or not this entry point is ever called.
+// the process exits, whether or not this entry point is ever called. "Loaded" is meant literally:
+// with CUDA's default lazy module loading the array gets its memory when the first kernel or
+// symbol of this translation unit is touched on a device — possibly the first call here — so a
+// caller that is about to give away all free memory makes one small call first (or sets
+// CUDA_MODULE_LOADING=EAGER); an out-of-memory answer at that point is reported as such.
 //
 // In host code `g_static_scratch` is only a handle for the symbol, not a device address; the
 // device address is fetched once per device with cudaGetSymbolAddress (with that device current)
@@ -520,8 +553,15 @@ unsigned char* static_scratch_ptr() {
         const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (err != cudaSuccess || ptr == nullptr) {
             cudaGetLastError();
-            set_last_errorf("flash_attn_decode_bf16_noalloc: cudaGetSymbolAddress failed: %s",
-                            cudaGetErrorString(err));
+            if (err == cudaErrorMemoryAllocation) {
+                // lazy module loading: this first call is what backs the array, and no memory is left for it
+                set_last_errorf("flash_attn_decode_bf16_noalloc: the library's %zu-byte scratch array could not be backed with "
+                                "device memory. CUDA loads device code lazily: make the first call on each device before "
+                                "the application reserves all device memory, or set CUDA_MODULE_LOADING=EAGER",
+                                kStaticScratchBytes);
+            } else {
+                set_last_errorf("flash_attn_decode_bf16_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+            }
             return nullptr;
         }
         g_static_ptr[dev] = static_cast<unsigned char*>(ptr);
@@ -595,7 +635,7 @@ int launch_static(const void* q, const void* k, const void* v, void* o, const in
     int rc = check_launch("decode_splitk_kernel");
     if (rc != FLASH_ATTN_OK) return rc;
     dim3 mgrid(q_heads, num_seqs);
-    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, context_lens, static_cast<T*>(o), q_heads,
+    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, context_lens, merge_out_single(o, q_heads), q_heads,
                                                       (int)chunk, max_splits);
     rc = check_launch("decode_merge_kernel");
     if (rc == FLASH_ATTN_OK) note_path("decode_splitk_static", 2);

@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -66,12 +67,17 @@ struct SharedStorage {
     unsigned long long s_full[2];   // MMA -> softmax: S_t ready (and every earlier MMA finished)
     unsigned long long p_lo[2];     // softmax -> MMA: keys 0-63 of P_t written, O_t rescaled
     unsigned long long p_hi[2];     // softmax -> MMA: keys 64-127 of P_t written
+    unsigned long long v_tail;      // copy engine -> V producer: the sequence's last, partly filled V tile has landed
+    unsigned long long drain;       // MMA issuer, error path only: every product issued so far has finished
     unsigned int tmem_base;
     volatile int abort_flag;
 };
 
 constexpr int kMaxPeers = 8;
+#ifdef FA_TRACE
 constexpr int kCtaLogEntries = 2048;
+#endif
+constexpr unsigned long long kWaitLimitNs = 2000000000ULL;   // default bound of every mbarrier wait
 
 struct PrefillArgs {
     // Output: n_out buffers of (batch, q_seq_len, o_heads, 128), each receiving this launch's heads
@@ -80,12 +86,19 @@ struct PrefillArgs {
     // NVLink), which makes the output all-gather part of the epilogue.
     void* o[kMaxPeers];
     int n_out, o_heads, o_head0;
-    int staged_store;   // 1 = stage O rows in shared memory and store whole rows (always with n_out > 1)
-    float* lse;
-    int* status;    // device word, set to non-zero when a bounded wait expired
+    int peer0;          // n_out > 1: the buffer this CTA's rows go to first; each CTA walks the buffers from there
+    float* lse;         // (batch, q_heads, q_seq_len) of this call, or null
+    float* lse_peers[kMaxPeers];   // n_lse > 0: (batch, o_heads, q_seq_len) on every GPU of the group, written at head o_head0
+    int n_lse;
+    int* status;        // word in mapped host memory, set to non-zero when a bounded wait expired
+    unsigned long long wait_ns;    // bound of every mbarrier wait
+    int test_skip_k;    // test hook: the K producer leaves out tile (test_skip_k - 1), so that a wait runs out; 0 = off
+#ifdef FA_TRACE
+    int staged_store;   // 1 = stage O rows in shared memory and store whole rows even for a single output
     long long* trace;  // optional timeline of one CTA (clock64 stamps), null unless the "prefill_trace" option is set
     int trace_y;       // blockIdx.y of the traced CTA (option "prefill_trace_y", default 0 = the heaviest)
     long long* cta_log;  // optional per-CTA {start ns, end ns, SM id} records ("prefill_trace" = 3), up to kCtaLogEntries
+#endif
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
     int band;       // tile pairs of one (batch, KV head) that sit next to each other in blockIdx.x
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
@@ -132,8 +145,10 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Bounded wait. Returns false when the wait was abandoned (time limit, or another thread of the
 // CTA already gave up); the caller then falls through to the end of the kernel.
+// The status word lives in mapped host memory (the host reads it without touching the device), so it
+// is written with a plain store: the code of one of the waits that expired.
 template <typename Storage>
-__device__ __forceinline__ bool mbar_wait(Storage& sm, unsigned long long* bar, unsigned parity, int* status,
+__device__ __forceinline__ bool mbar_wait(Storage& sm, unsigned long long* bar, unsigned parity, const PrefillArgs& a,
                                           int where) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
@@ -141,9 +156,10 @@ __device__ __forceinline__ bool mbar_wait(Storage& sm, unsigned long long* bar, 
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (sm.abort_flag) return false;
-            if (global_timer_ns() - t0 > 2000000000ULL) {
+            if (global_timer_ns() - t0 > a.wait_ns) {
                 sm.abort_flag = 1;
-                atomicCAS(status, 0, where);
+                *reinterpret_cast<volatile int*>(a.status) = where;
+                __threadfence_system();
                 return false;
             }
         }
@@ -329,10 +345,16 @@ __device__ __forceinline__ unsigned make_idesc(bool b_mn_major, int n) {
 }
 
 // Timeline slots: role (0/1 = softmax warpgroup, 2 = MMA issuer) x kv step (< 60) x event (< 8).
-constexpr int kTraceSteps = 60;
+// Compiled in with -DFA_TRACE only; the default build carries none of it.
+[[maybe_unused]] constexpr int kTraceSteps = 60;
+#ifdef FA_TRACE
 __device__ __forceinline__ void trace_event(long long* trace, int role, int j, int ev) {
     if (trace != nullptr && j < kTraceSteps) trace[(role * kTraceSteps + j) * 8 + ev] = clock64();
 }
+#define FA_TRACE_EVENT(role, j, ev) trace_event(trace, role, j, ev)
+#else
+#define FA_TRACE_EVENT(role, j, ev) ((void)0)
+#endif
 
 struct TileInfo {
     int valid;    // this query tile exists
@@ -441,8 +463,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     extern __shared__ unsigned char smem_raw[];
     using Storage = SharedStorage<D>;
     Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+#ifdef FA_TRACE
     const long long t_entry = clock64();
     const unsigned long long ns_entry = a.cta_log != nullptr ? global_timer_ns() : 0ULL;
+#endif
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -492,6 +516,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mbar_init(&sm.v_full[i], 1);
             mbar_init(&sm.v_empty[i], 1);
         }
+        mbar_init(&sm.v_tail, 1);
+        mbar_init(&sm.drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         auto load_q = [&](const TileInfo& ti, int t) {
@@ -504,10 +530,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             load_kv_tile<D>(a, sq, b, kvh, dst, map, bar, j);
         };
         load_q(t0, 0);
-        if (n_pre > 0 && !kv_edge(0)) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
+        if (n_pre > 0 && !kv_edge(0) && a.test_skip_k != 1) load_kv(sm.k[0], &k_map, &sm.k_full[0], 0);
         load_q(t1, 1);
         for (int j = 1; j < n_pre; ++j)
-            if (!kv_edge(j)) load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
+            if (!kv_edge(j) && a.test_skip_k != j + 1) load_kv(sm.k[j], &k_map, &sm.k_full[j], j);
         // the V tiles come from a producer thread of their own (warp kLoadWarpV), after the set-up barrier
     }
     if (warp == kMmaWarp) {
@@ -518,16 +544,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = sm.tmem_base;
-    // Register budget: the kernel is compiled for 168 registers per thread (384 threads); the
-    // producer/issuer warpgroup hands most of its share to the two softmax warpgroups, which
-    // keep a whole 128-column score row per thread in registers.
+#ifdef FA_TRACE
     // only the heaviest CTA of the first (batch, KV head) records its timeline, one thread per role
     long long* const trace = (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == (unsigned)a.trace_y && lane == 0 && (warp == kMmaWarp || (warp & 3) == 0)) ? a.trace : nullptr;
     // slot kTraceSteps - 1 of each role holds the CTA's life cycle instead of a kv step
     if (trace != nullptr && warp == kMmaWarp) {
         trace[(2 * kTraceSteps + kTraceSteps - 1) * 8 + 0] = t_entry;
-        trace_event(trace, 2, kTraceSteps - 1, 1);   // set-up (barriers, tensor memory) done
+        FA_TRACE_EVENT(2, kTraceSteps - 1, 1);   // set-up (barriers, tensor memory) done
     }
+#endif
 
     // Register budget: the kernel is compiled for 168 registers per thread (384 threads); the
     // producer/issuer warpgroup hands most of its share to the two softmax warpgroups, which
@@ -555,29 +580,67 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 for (int j = 0; j < n_pre; ++j)
                     if (kv_edge(j)) edge_tile_copy<D>(sm.k[j], a.k, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &sm.k_full[j], lane);
             }
+            // The sequence's last V tile, when the sequence does not end on a tile boundary, holds rows
+            // that are not this sequence's: the unwritten rest of its last page, or the next sequence
+            // of a packed buffer. P is exactly zero there, but 0 x NaN (an uninitialised pool, a page
+            // recycled from other use) would still poison the whole output row, so those rows are
+            // cleared in shared memory before the tile is handed to the MMA issuer: its copy completes
+            // on a barrier of its own, the producer warp zeroes the rows and then completes the
+            // ring's barrier with a plain arrival. (Garbage in K is harmless: the score mask is a select.)
+            const bool tail_fix = is_v && (a.paged || packed) && (sq.kv_len % kBlockN) != 0;
+            const int tail_j = sq.kv_len > 0 ? (sq.kv_len - 1) / kBlockN : -1;
+            bool tail_pending = false;   // the tail tile's copy was issued and v_tail not yet seen complete
             int issued = is_v ? 0 : n_pre;   // K tiles 0 .. n_pre-1 were issued during set-up
             for (int j = issued; j < n_max && alive; ++j) {
                 const int s = j % kStages;
                 if (j >= kStages) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a.status, is_v ? 2 : 1));
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a, is_v ? 2 : 1));
                     if (!alive) break;
                 }
-                if (kv_edge(j)) edge_tile_copy<D>(ring[s], kv_base, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &full[s], lane);
-                else if (lane == 0) load_kv_tile<D>(a, sq, b, kvh, ring[s], map, &full[s], j);
+                const bool fix = tail_fix && j == tail_j;
+                unsigned long long* const bar = fix ? &sm.v_tail : &full[s];
+                if (!is_v && a.test_skip_k == j + 1) {
+                    // test hook: this tile is never requested, the issuer's wait for it runs out
+                } else if (kv_edge(j)) {
+                    edge_tile_copy<D>(ring[s], kv_base, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, bar, lane);
+                } else if (lane == 0) {
+                    load_kv_tile<D>(a, sq, b, kvh, ring[s], map, bar, j);
+                }
                 issued = j + 1;
+                if (fix) {
+                    tail_pending = true;
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.v_tail, 0u, a, 4));
+                    if (!alive) break;
+                    tail_pending = false;
+                    const int first = sq.kv_len - j * kBlockN;   // first row of the tile that is not this sequence's
+                    constexpr int kChunksPerHalfRow = 8;        // 128 B per row and 64-column half
+                    const int n_chunks = (kBlockN - first) * kChunksPerHalfRow;
+                    for (int h = 0; h < D / 64; ++h)
+                        for (int idx = lane; idx < n_chunks; idx += 32)
+                            *reinterpret_cast<uint4*>(ring[s] + h * kHalfBytes + first * 128 + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
             }
             // Make sure none of this warp's copies is still in flight when the CTA exits: wait
             // (bounded) for the last fill of every stage (and of the Q tiles). These waits ignore the
             // abort flag: they only depend on the copy engine.
             if (lane == 0) {
                 if (!is_v) {
-                    if (t0.valid) mbar_wait(sm, &sm.q_full[0], 0, a.status, 3);
-                    if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a.status, 3);
+                    if (t0.valid) mbar_wait(sm, &sm.q_full[0], 0, a, 3);
+                    if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a, 3);
                 }
                 const unsigned long long t_begin = global_timer_ns();
                 for (int s = 0; s < kStages; ++s) {
                     if (issued <= s) continue;   // never filled
                     const int last = issued - 1 - (issued - 1 - s) % kStages;   // last issued tile of this stage
+                    if (!is_v && a.test_skip_k == last + 1) continue;          // test hook: never requested
+                    if (tail_fix && last == tail_j) {
+                        // that tile's copy completes on v_tail; the ring's barrier got (or, after an abort, never gets) a plain arrival
+                        while (tail_pending && !mbar_try_wait(&sm.v_tail, 0u) && global_timer_ns() - t_begin < 100000000ULL) {}
+                        continue;
+                    }
                     while (!mbar_try_wait(&full[s], (unsigned)(last / kStages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
                 }
             }
@@ -622,9 +685,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             };
             for (int t = 0; t < 2 && alive; ++t)
-                if (ts[t].valid) alive = (mbar_wait(sm, &sm.q_full[t], 0, a.status, 10));
-            if (alive && n_max > 0) alive = (mbar_wait(sm, &sm.k_full[0], 0, a.status, 11));
-            trace_event(trace, 2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
+                if (ts[t].valid) alive = (mbar_wait(sm, &sm.q_full[t], 0, a, 10));
+            if (alive && n_max > 0) alive = (mbar_wait(sm, &sm.k_full[0], 0, a, 11));
+            FA_TRACE_EVENT(2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
             if (alive && n_max > 0) {
                 tc_fence_after();
                 for (int t = 0; t < 2; ++t) {
@@ -640,34 +703,41 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const unsigned ph = (unsigned)(j / kStages) & 1u;
                 const int s1 = (j + 1) % kStages;
                 const unsigned ph1 = (unsigned)((j + 1) / kStages) & 1u;
-                alive = (mbar_wait(sm, &sm.v_full[s], ph, a.status, 13));
+                alive = (mbar_wait(sm, &sm.v_full[s], ph, a, 13));
                 if (!alive) break;
                 bool k_seen = j + 1 >= n_max;   // K(j+1) is first needed for S(j+1): looked at while P's second half is awaited
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
                     // the first 64 keys of P_t arrive while the softmax still works on the other 64:
                     // their half of P.V leaves the critical path
-                    alive = (mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a.status, 14 + t));
+                    alive = (mbar_wait(sm, &sm.p_lo[t], (unsigned)j & 1u, a, 14 + t));
                     if (!alive) break;
-                    trace_event(trace, 2, j, t * 2);
+                    FA_TRACE_EVENT(2, j, t * 2);
                     tc_fence_after();
                     issue_pv(t, s, j > 0, 0);
                     if (!k_seen) {
-                        alive = (mbar_wait(sm, &sm.k_full[s1], ph1, a.status, 12));
+                        alive = (mbar_wait(sm, &sm.k_full[s1], ph1, a, 12));
                         if (!alive) break;
                         k_seen = true;
                     }
-                    alive = (mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a.status, 16 + t));
+                    alive = (mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a, 16 + t));
                     if (!alive) break;
                     tc_fence_after();
                     issue_pv(t, s, true, 1);
                     if (j + 1 < ts[t].n_kv) issue_s(t, s1);
                     tc_commit(&sm.s_full[t]);   // S_t(j+1) ready, or after the last PV: O_t final
-                    trace_event(trace, 2, j, t * 2 + 1);
+                    FA_TRACE_EVENT(2, j, t * 2 + 1);
                 }
                 if (!alive) break;
                 tc_commit(&sm.v_empty[s]);
                 if (j + 1 < n_max) tc_commit(&sm.k_empty[s1]);
+            }
+            if (!alive) {
+                // error path: tensor memory is freed at the end of the kernel, so let every product issued
+                // so far finish first (bounded; depends on the tensor pipe alone)
+                tc_commit(&sm.drain);
+                const unsigned long long t_begin = global_timer_ns();
+                while (!mbar_try_wait(&sm.drain, 0u) && global_timer_ns() - t_begin < 100000000ULL) {}
             }
         }
     }
@@ -687,9 +757,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         bool alive = true;
 
         for (int j = 0; j < ti.n_kv && alive; ++j) {
-            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a.status, 20 + t));
+            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)j & 1u, a, 20 + t));
             if (!alive) break;
-            trace_event(trace, t, j, 0);
+            FA_TRACE_EVENT(t, j, 0);
             tc_fence_after();
             const int key0 = j * kBlockN;
             // mask only where the causal diagonal or the end of K/V cuts through this tile
@@ -746,7 +816,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     }
                 }
                 float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
-                trace_event(trace, t, j, 1);
+                FA_TRACE_EVENT(t, j, 1);
                 float alpha = 1.0f;
                 bool changed = false;
                 if (mx > m + kRescaleThreshold) {
@@ -809,7 +879,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.p_lo[t]);
-                trace_event(trace, t, j, 2);
+                FA_TRACE_EVENT(t, j, 2);
                 mbar_arrive(&sm.p_hi[t]);
                 float sum_lo, sum_hi;
                 unpack2(sum2, sum_lo, sum_hi);
@@ -842,7 +912,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], sv[c][i], sv[c][i + 1]);
                 float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 mx *= a.scale_log2;   // scale > 0 is guaranteed by the dispatcher
-                trace_event(trace, t, j, 1);
+                FA_TRACE_EVENT(t, j, 1);
 
                 float alpha = 1.0f;
                 bool changed = false;
@@ -896,7 +966,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         tc_wait_st();
                         tc_fence_before();
                         mbar_arrive(c == 0 ? &sm.p_lo[t] : &sm.p_hi[t]);
-                        if (c == 0) trace_event(trace, t, j, 2);
+                        if (c == 0) FA_TRACE_EVENT(t, j, 2);
                     }
                 };
                 if (need_mask || (kMask && pad)) exp_phase(std::false_type{});
@@ -906,12 +976,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 const float sum = sum_lo + sum_hi;
                 l = l * alpha + sum;
             }
-            trace_event(trace, t, j, 3);
+            FA_TRACE_EVENT(t, j, 3);
         }
 
         // epilogue: O_t is final once the commit after the last P.V has arrived
         if (alive && ti.n_kv > 0)
-            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a.status, 30 + t));
+            alive = __all_sync(0xffffffffu, mbar_wait(sm, &sm.s_full[t], (unsigned)ti.n_kv & 1u, a, 30 + t));
         if (alive && ti.valid) {
             tc_fence_after();
             const bool row_ok = row < sq.q_len;
@@ -922,7 +992,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // a bulk store writes every row of its box that lies inside the tensor: in a packed buffer the
             // rows after this sequence belong to the next one, so a tile that overhangs the end of its
             // sequence takes the row-guarded path
-            const bool bulk_ok = a.n_out == 1 && !a.staged_store && (a.mode != MODE_VARLEN || ti.row0 + kBlockM <= sq.q_len);
+#ifdef FA_TRACE
+            const bool staged_only = a.staged_store != 0;
+#else
+            constexpr bool staged_only = false;
+#endif
+            const bool bulk_ok = a.n_out == 1 && !staged_only && (a.mode != MODE_VARLEN || ti.row0 + kBlockM <= sq.q_len);
             if (bulk_ok) {
                 // Single output: the rows go out as bulk tensor stores. Each warp lays its 32 rows down in
                 // the Q tile's shared memory (every MMA that read Q_t has finished) in the 128-byte-swizzled
@@ -1004,27 +1079,36 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         if (grow < sq.q_len) {
                             const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * kRowBytes + ((ch ^ (rr & (kChunks - 1))) << 4));
                             const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * D + ch * 8;
-                            for (int pe = 0; pe < a.n_out; ++pe)
+                            // every GPU of a group starts its walk at a different buffer (peer0 = its own
+                            // index + 1), so that at no time all of them store to the same GPU
+                            int pe = a.peer0;
+                            for (int n = 0; n < a.n_out; ++n) {
                                 *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
+                                pe = pe + 1 == a.n_out ? 0 : pe + 1;
+                            }
                         }
                     }
                 }
             }
-            if (row_ok && a.lse != nullptr) {
-                a.lse[((long long)b * a.q_heads + ti.head) * a.q_seq_len + row] =
-                    (l > 0.0f && q_ok) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            if (row_ok && (a.lse != nullptr || a.n_lse > 0)) {
+                const float lse_val = (l > 0.0f && q_ok) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                if (a.lse != nullptr) a.lse[((long long)b * a.q_heads + ti.head) * a.q_seq_len + row] = lse_val;
+                // head-sharded call: the same value into the (batch, o_heads, q_seq_len) LSE of every GPU of the group
+                const long long g_off = ((long long)b * a.o_heads + a.o_head0 + ti.head) * a.q_seq_len + row;
+                for (int n = 0; n < a.n_lse; ++n) a.lse_peers[n][g_off] = lse_val;
             }
-            trace_event(trace, t, kTraceSteps - 1, 0);       // epilogue stores issued
+            FA_TRACE_EVENT(t, kTraceSteps - 1, 0);       // epilogue stores issued
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    trace_event(trace, 2, kTraceSteps - 1, 3);               // every role done
+    FA_TRACE_EVENT(2, kTraceSteps - 1, 3);               // every role done
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
     }
+#ifdef FA_TRACE
     if (a.cta_log != nullptr && threadIdx.x == 0) {
         const int idx = blockIdx.y * gridDim.x + blockIdx.x;
         if (idx < kCtaLogEntries) {
@@ -1035,6 +1119,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             a.cta_log[idx * 3 + 2] = (long long)smid;
         }
     }
+#endif
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -1096,26 +1181,51 @@ bool encode_paged_map(CUtensorMap* map, const void* base, int dtype, int d, int 
     return rc == CUDA_SUCCESS;
 }
 
-// Per-device debug area: the status word, then (from byte 256) the optional timeline.
-constexpr size_t kDebugBytes = 16384 + kCtaLogEntries * 24;
+// Status words, one per device, in mapped pinned host memory: a kernel whose bounded wait ran out
+// stores the wait's code there, and the host reads it at the next entry-point call without
+// touching the device. One portable allocation for all devices, a cache line per device.
+constexpr int kMaxDevices = 64;
+constexpr int kStatusStride = 32;   // ints (128 bytes) between two devices' words
 std::mutex g_status_mutex;
-int* g_status_word[64] = {nullptr};
+int* g_status_host = nullptr;
 
 int* status_word() {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     std::lock_guard<std::mutex> lock(g_status_mutex);
-    if (g_status_word[dev] == nullptr) {
-        int* p = nullptr;
+    if (g_status_host == nullptr) {
+        void* p = nullptr;
+        if (cudaHostAlloc(&p, sizeof(int) * kStatusStride * kMaxDevices, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        std::memset(p, 0, sizeof(int) * kStatusStride * kMaxDevices);
+        g_status_host = static_cast<int*>(p);
+    }
+    return g_status_host + dev * kStatusStride;
+}
+
+#ifdef FA_TRACE
+// Per-device debug area in device memory: (from byte 256) the optional timeline, from byte 16384 the CTA log.
+constexpr size_t kDebugBytes = 16384 + kCtaLogEntries * 24;
+unsigned char* g_debug_area[kMaxDevices] = {nullptr};
+
+unsigned char* debug_area() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (g_debug_area[dev] == nullptr) {
+        void* p = nullptr;
         if (cudaMalloc(&p, kDebugBytes) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
         cudaMemset(p, 0, kDebugBytes);
-        g_status_word[dev] = p;
+        g_debug_area[dev] = static_cast<unsigned char*>(p);
     }
-    return g_status_word[dev];
+    return g_debug_area[dev];
 }
+#endif
 
 template <typename T, int D, bool kMask>
 int launch_typed(const AttnParams& p, cudaStream_t stream) {
@@ -1125,9 +1235,11 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     const int q_batch = packed ? 1 : p.num_seqs, q_rows = packed ? p.total_q : p.q_seq_len;
     const int k_batch = packed ? 1 : p.num_seqs, k_rows = packed ? p.total_k : p.kv_seq_len;
     bool ok = encode_map(&qm, p.q, p.dtype, D, q_batch, q_rows, p.q_heads);
-    // the output as 32-row boxes (one per softmax warp); only used when there is a single output buffer
-    ok = ok && encode_map(&om, p.n_out > 0 ? p.o_peers[0] : p.o, p.dtype, D, q_batch, q_rows,
-                          p.n_out > 0 ? p.o_heads : p.q_heads, 32);
+    // The output as 32-row boxes (one per softmax warp). Bulk stores are used for a single, local output
+    // only: a head-sharded call (n_out > 0) stores every copy with plain stores, and no tensor map is
+    // ever made over another GPU's memory — the kernel's fourth map is then a second one over q, unused.
+    if (p.n_out > 0) om = qm;
+    else ok = ok && encode_map(&om, p.o, p.dtype, D, q_batch, q_rows, p.q_heads, 32);
     if (p.paged) {
         ok = ok && encode_paged_map(&km, p.k, p.dtype, D, p.block_size, p.kv_heads) &&
              encode_paged_map(&vm, p.v, p.dtype, D, p.block_size, p.kv_heads);
@@ -1141,11 +1253,15 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
 
     PrefillArgs a{};
     if (p.n_out > 0) {
-        if (p.n_out > kMaxPeers) return -1;
+        if (p.n_out > kMaxPeers || p.n_lse > kMaxPeers) return -1;
         for (int i = 0; i < p.n_out; ++i) a.o[i] = p.o_peers[i];
+        for (int i = 0; i < p.n_lse; ++i) a.lse_peers[i] = p.lse_peers[i];
         a.n_out = p.n_out;
+        a.n_lse = p.n_lse;
         a.o_heads = p.o_heads;
         a.o_head0 = p.o_head0;
+        // with equal shards this GPU's index in the group is o_head0 / q_heads: start one past it
+        a.peer0 = (p.o_head0 / p.q_heads + 1) % p.n_out;
     } else {
         a.o[0] = p.o;
         a.n_out = 1;
@@ -1154,10 +1270,17 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     }
     a.lse = p.lse;
     a.status = status;
-    a.staged_store = get_option_prefill_trace() == 2 ? 1 : 0;
-    a.trace_y = get_option_prefill_trace_y();
-    a.cta_log = get_option_prefill_trace() == 3 ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 16384) : nullptr;
-    a.trace = get_option_prefill_trace() == 1 ? reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(status) + 256) : nullptr;
+    a.wait_ns = get_option_prefill_wait_us() > 0 ? (unsigned long long)get_option_prefill_wait_us() * 1000ULL : kWaitLimitNs;
+    a.test_skip_k = get_option_prefill_test_skip_k();
+#ifdef FA_TRACE
+    {
+        unsigned char* dbg = get_option_prefill_trace() != 0 ? debug_area() : nullptr;
+        a.staged_store = get_option_prefill_trace() == 2 ? 1 : 0;
+        a.trace_y = get_option_prefill_trace_y();
+        a.cta_log = (dbg != nullptr && get_option_prefill_trace() == 3) ? reinterpret_cast<long long*>(dbg + 16384) : nullptr;
+        a.trace = (dbg != nullptr && get_option_prefill_trace() == 1) ? reinterpret_cast<long long*>(dbg + 256) : nullptr;
+    }
+#endif
     a.batch = p.num_seqs;
     a.q_seq_len = p.q_seq_len;
     a.kv_seq_len = p.kv_seq_len;
@@ -1210,27 +1333,42 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-int prefill_device_status() {
+int prefill_take_status() {
     int* status = status_word();
-    if (status == nullptr) return -1;
-    int h = 0;
-    if (cudaMemcpy(&h, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
-        cudaGetLastError();
-        return -1;
-    }
-    if (h != 0) cudaMemset(status, 0, sizeof(int));
+    if (status == nullptr) return 0;
+    volatile int* w = status;
+    const int h = *w;
+    if (h != 0) *w = 0;
     return h;
 }
 
-int prefill_debug_read(void* dst, int bytes) {
+int prefill_device_status() {
     int* status = status_word();
-    if (status == nullptr || dst == nullptr || bytes <= 0) return -1;
-    const size_t n = (size_t)bytes < kDebugBytes ? (size_t)bytes : kDebugBytes;
-    if (cudaMemcpy(dst, status, n, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    if (status == nullptr) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) {
         cudaGetLastError();
         return -1;
     }
+    return prefill_take_status();
+}
+
+int prefill_debug_read(void* dst, int bytes) {
+#ifdef FA_TRACE
+    unsigned char* dbg = debug_area();
+    int* status = status_word();
+    if (dbg == nullptr || status == nullptr || dst == nullptr || bytes <= 0) return -1;
+    const size_t n = (size_t)bytes < kDebugBytes ? (size_t)bytes : kDebugBytes;
+    if (cudaMemcpy(dst, dbg, n, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    if (n >= sizeof(int)) std::memcpy(dst, status, sizeof(int));
     return (int)n;
+#else
+    (void)dst;
+    (void)bytes;
+    return -1;   // the timeline is compiled in with -DFA_TRACE only
+#endif
 }
 
 int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {

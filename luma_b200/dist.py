@@ -62,38 +62,56 @@ def all_gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
 
 class PeerOutput:
     """The full attention output (B, S, Hq_total, d), allocated on every rank and mapped into every
-    other rank of the group through CUDA IPC, so that a kernel on one GPU can store its heads
-    straight into all copies (plain stores over NVLink; nothing here uses TMA or multicast).
+    other rank of the group through CUDA IPC (luma_ipc_export / luma_ipc_open of the C ABI), so that
+    a kernel on one GPU can store its heads straight into all copies (plain stores over NVLink;
+    nothing here uses TMA or multicast). With `with_lse` a (B, Hq_total, S) f32 log-sum-exp tensor
+    is shared the same way.
 
-    `fused_attention` runs the head-sharded prefill with the gather fused into its epilogue and
-    then synchronises the group, after which `self.out` holds every rank's heads.
+    `fused_attention` runs the head-sharded prefill with the gather fused into its epilogue,
+    `fused_decode` the head-sharded single-token decode with the gather fused into its merge kernel;
+    `sync()` then synchronises the group, after which `self.out` (and `self.lse`) hold every rank's heads.
     """
 
-    def __init__(self, group, shape, dtype, device):
-        from torch.multiprocessing.reductions import reduce_tensor
+    def __init__(self, group, shape, dtype, device, with_lse=False):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.out = torch.empty(shape, dtype=dtype, device=device)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.out), group=group)
-        self.peers = []          # keeps the mappings alive
-        self.ptrs = []
-        for r, (fn, args) in enumerate(handles):
-            if r == self.rank:
-                self.ptrs.append(self.out.data_ptr())
-                continue
-            args = list(args)
-            args[6] = device.index if isinstance(device, torch.device) else int(device)  # map on MY device
-            t = fn(*args)
-            self.peers.append(t)
-            self.ptrs.append(t.data_ptr())
+        self.lse = torch.empty((shape[0], shape[2], shape[1]), dtype=torch.float32, device=device) if with_lse else None
+        self._opened = []        # mapped peer pointers, closed by close()
+        self.ptrs = self._exchange(self.out)
+        self.lse_ptrs = self._exchange(self.lse) if with_lse else None
         self._flag = torch.zeros(1, device=device)
         dist.barrier(group=group)
 
-    def fused_attention(self, q, k, v, q_heads_total, q_head_offset, start_pos=0, scale=None, row0=0, lse=None):
+    def _exchange(self, t):
+        """Every rank's device pointer to its own copy of `t`, as seen from THIS process."""
+        import ctypes
+        from . import ffi
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_longlong(0)
+        if ffi.lib.luma_ipc_export(t.data_ptr(), handle, ctypes.byref(offset)) != 0:
+            raise RuntimeError(ffi.lib.luma_comm_last_error().decode())
+        mine = (handle.raw, int(offset.value))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        ptrs = []
+        for r, (h, off) in enumerate(everyone):
+            if r == self.rank:
+                ptrs.append(t.data_ptr())
+                continue
+            p = ctypes.c_void_p()
+            if ffi.lib.luma_ipc_open(ctypes.c_char_p(h), off, ctypes.byref(p)) != 0:
+                raise RuntimeError(ffi.lib.luma_comm_last_error().decode())
+            self._opened.append(p.value)
+            ptrs.append(p.value)
+        return ptrs
+
+    def fused_attention(self, q, k, v, q_heads_total, q_head_offset, start_pos=0, scale=None, row0=0, lse=None,
+                        gather_lse=False):
         """q (B, Sq, Hq_local, d), k/v (B, Skv, Hkv_local, d): this rank's shard. Writes rows
-        [row0, row0 + Sq) of every rank's output. Call `sync()` before reading `self.out`."""
+        [row0, row0 + Sq) of every rank's output (and, with `gather_lse`, this rank's heads of every
+        rank's LSE; whole sequences only). Call `sync()` before reading `self.out`."""
         from . import low
         b, sq, hq_l, d = q.shape
         skv, hkv_l = k.shape[1], k.shape[2]
@@ -106,8 +124,23 @@ class PeerOutput:
         # stride then never matters because batch == 1
         ptrs = [p + off for p in self.ptrs]
         assert sq + row0 <= s_total
+        lse_ptrs = None
+        if gather_lse:
+            assert self.lse_ptrs is not None and row0 == 0 and sq == s_total
+            lse_ptrs = self.lse_ptrs
         low.flash_attn_allgather(q, k, v, ptrs, q_heads_total, q_head_offset, b, sq, skv, hq_l, hkv_l, d,
-                                 int(start_pos), scale, None, lse)
+                                 int(start_pos), scale, None, lse, lse_ptrs)
+
+    def fused_decode(self, q, k_cache, v_cache, block_tables, context_lens, q_heads_total, q_head_offset, scale=None):
+        """q (B, 1, Hq_local, d) and this rank's cache slice (num_blocks, page, Hkv_local, d): one
+        decode step whose merge kernel writes this rank's heads into every rank's (B, 1, Hq_total, d)."""
+        from . import low
+        b, one, hq_l, d = q.shape
+        assert one == 1 and tuple(self.out.shape) == (b, 1, q_heads_total, d)
+        scale = float(scale) if scale is not None else 1.0 / (d ** 0.5)
+        low.flash_attn_with_kvcache_allgather(q, k_cache, v_cache, self.ptrs, q_heads_total, q_head_offset, block_tables,
+                                              context_lens, b, hq_l, k_cache.shape[2], d, k_cache.shape[1],
+                                              block_tables.shape[1], scale)
 
     def sync(self):
         """Every rank's stores have landed everywhere once all ranks passed this point."""
@@ -117,9 +150,13 @@ class PeerOutput:
     def close(self):
         """Drops the mappings of the peers' buffers. Collective: every rank calls it, after which no
         rank touches another rank's buffer again, so the owners may free them in any order."""
+        from . import ffi
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
-        self.peers.clear()
+        for p in self._opened:
+            ffi.lib.luma_ipc_close(p)
+        self._opened = []
         self.ptrs = [self.out.data_ptr()]
+        self.lse_ptrs = None
         torch.cuda.synchronize()
         dist.barrier(group=self.group)

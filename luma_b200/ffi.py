@@ -38,10 +38,17 @@ EXPORTED_SYMBOLS = (
     + ["flash_attn_last_error"]
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
     + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather",
-       "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total"]
+       "flash_attn_f16_allgather_lse", "flash_attn_bf16_allgather_lse",
+       "flash_attn_with_kvcache_f16_allgather", "flash_attn_with_kvcache_bf16_allgather",
+       "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total",
+       "flash_attn_release_workspaces"]
     + [f"luma_softmax_{s}" for s in DTYPE_SUFFIX]   # include/luma_nn_kernels.h
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
+    # include/luma_dist_comm.h
+    + ["luma_comm_unique_id", "luma_comm_from_rank", "luma_comm_from_devices", "luma_comm_rank", "luma_comm_world_size",
+       "luma_comm_device", "luma_comm_all_gather", "luma_comm_barrier", "luma_comm_destroy", "luma_ipc_export",
+       "luma_ipc_open", "luma_ipc_close", "luma_comm_last_error"]
 )
 
 for _s in DTYPE_SUFFIX:
@@ -71,6 +78,30 @@ for _s in ("f16", "bf16"):
                                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                           c_float, c_void_p]
     getattr(lib, f"flash_attn_{_s}_allgather").restype = c_int
+    getattr(lib, f"flash_attn_{_s}_allgather_lse").argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                              c_float, c_void_p]
+    getattr(lib, f"flash_attn_{_s}_allgather_lse").restype = c_int
+    getattr(lib, f"flash_attn_with_kvcache_{_s}_allgather").argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                                       c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                                       c_int, c_int, c_float, c_void_p]
+    getattr(lib, f"flash_attn_with_kvcache_{_s}_allgather").restype = c_int
+lib.flash_attn_release_workspaces.argtypes = []
+lib.flash_attn_release_workspaces.restype = c_int
+lib.luma_comm_unique_id.argtypes = [c_void_p]
+lib.luma_comm_from_rank.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int]
+lib.luma_comm_from_devices.argtypes = [c_void_p, c_int, c_void_p]
+lib.luma_comm_rank.argtypes = [c_void_p]
+lib.luma_comm_world_size.argtypes = [c_void_p]
+lib.luma_comm_device.argtypes = [c_void_p]
+lib.luma_comm_all_gather.argtypes = [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p]
+lib.luma_comm_barrier.argtypes = [c_void_p, c_void_p]
+lib.luma_comm_destroy.argtypes = [c_void_p]
+lib.luma_ipc_export.argtypes = [c_void_p, c_void_p, c_void_p]
+lib.luma_ipc_open.argtypes = [c_void_p, ctypes.c_longlong, c_void_p]
+lib.luma_ipc_close.argtypes = [c_void_p]
+lib.luma_comm_last_error.argtypes = []
+lib.luma_comm_last_error.restype = c_char_p
 lib.flash_attn_kvcache_append.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
 lib.flash_attn_kvcache_append.restype = c_int

@@ -147,10 +147,13 @@ def debug_block_slots(block_tables, context_lens, offsets, num_seqs, block_size,
 
 
 def flash_attn_allgather(q, k, v, o_peer_ptrs, q_heads_total, q_head_offset, batch, q_seq_len, kv_seq_len,
-                         q_num_heads, kv_num_heads, head_size, start_pos, scale, stream=None, lse=None) -> None:
+                         q_num_heads, kv_num_heads, head_size, start_pos, scale, stream=None, lse=None,
+                         lse_peer_ptrs=None) -> None:
     """Head-sharded prefill whose epilogue stores this rank's heads into the full output buffer of
-    every GPU of the group (`o_peer_ptrs`: device pointers, own buffer included). Additive; the
-    reference runs attention and luma-dist's all_gather as two separate steps."""
+    every GPU of the group (`o_peer_ptrs`: device pointers, own buffer included). With
+    `lse_peer_ptrs` the log-sum-exp is gathered the same way into every GPU's (batch, q_heads_total,
+    q_seq_len) f32 tensor. Additive; the reference runs attention and luma-dist's all_gather as two
+    separate steps."""
     import ctypes
     sfx = _suffix(q)
     if sfx == "f32":
@@ -162,9 +165,37 @@ def flash_attn_allgather(q, k, v, o_peer_ptrs, q_heads_total, q_head_offset, bat
     _check_len("v", v.numel(), kv_need)
     n = len(o_peer_ptrs)
     arr = (ctypes.c_void_p * n)(*[int(p) for p in o_peer_ptrs])
-    code = getattr(ffi.lib, f"flash_attn_{sfx}_allgather")(
-        _ptr(q), _ptr(k), _ptr(v), ctypes.cast(arr, ctypes.c_void_p), n, q_heads_total, q_head_offset, _ptr(lse),
-        batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, _stream_ptr(stream, q))
+    if lse_peer_ptrs is not None:
+        if len(lse_peer_ptrs) != n:
+            raise E.InvalidShape("flash_attn_allgather: lse_peer_ptrs must have one entry per output buffer")
+        larr = (ctypes.c_void_p * n)(*[int(p) for p in lse_peer_ptrs])
+        code = getattr(ffi.lib, f"flash_attn_{sfx}_allgather_lse")(
+            _ptr(q), _ptr(k), _ptr(v), ctypes.cast(arr, ctypes.c_void_p), ctypes.cast(larr, ctypes.c_void_p), n,
+            q_heads_total, q_head_offset, batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos,
+            scale, _stream_ptr(stream, q))
+    else:
+        code = getattr(ffi.lib, f"flash_attn_{sfx}_allgather")(
+            _ptr(q), _ptr(k), _ptr(v), ctypes.cast(arr, ctypes.c_void_p), n, q_heads_total, q_head_offset, _ptr(lse),
+            batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
+
+
+def flash_attn_with_kvcache_allgather(q, k_cache, v_cache, o_peer_ptrs, q_heads_total, q_head_offset, block_tables,
+                                      context_lens, num_seqs, q_heads, kv_heads, head_size, block_size, max_blocks,
+                                      scale, stream=None) -> None:
+    """Head-sharded single-token paged decode whose merge kernel stores this rank's heads into the
+    (num_seqs, 1, q_heads_total, head_size) output of every GPU of the group. Additive."""
+    import ctypes
+    sfx = _suffix(q)
+    if sfx == "f32":
+        raise E.Unsupported("flash_attn_with_kvcache_allgather: f16/bf16 only")
+    _check_len("q", q.numel(), num_seqs * q_heads * head_size)
+    n = len(o_peer_ptrs)
+    arr = (ctypes.c_void_p * n)(*[int(p) for p in o_peer_ptrs])
+    code = getattr(ffi.lib, f"flash_attn_with_kvcache_{sfx}_allgather")(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), ctypes.cast(arr, ctypes.c_void_p), n, q_heads_total, q_head_offset,
+        _ptr(block_tables), _ptr(context_lens), num_seqs, q_heads, kv_heads, head_size, block_size, max_blocks, scale,
+        _stream_ptr(stream, q))
     E.from_status(code, ffi.last_error())
 
 

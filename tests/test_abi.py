@@ -14,11 +14,11 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _header_functions():
-    """Every function the C headers under include/ declare (flash_attn.h, luma_nn_kernels.h)."""
+    """Every function the C headers under include/ declare (flash_attn.h, luma_nn_kernels.h, luma_dist_comm.h)."""
     names = set()
     for h in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
-        names |= set(re.findall(r"\b((?:flash_attn|luma_softmax)_\w+)\s*\(", text))
+        names |= set(re.findall(r"\b((?:flash_attn|luma_softmax|luma_comm|luma_ipc)_\w+)\s*\(", text))
     return sorted(names)
 
 
