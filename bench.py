@@ -3,16 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--only NAME]
 
-Prints ONE JSON line. A "step" is one pass of the primary workload (BASELINE.json configs[1]:
-causal bf16 prefill B=4, Hq=Hkv=32, S=2048, d=128 with fp32 LSE). With N > 1 (torchrun, one rank
-per GPU) every rank owns 32 query/KV heads of a 32*N-head layer (weak scaling), runs the same
-kernel on its shard and the outputs are joined by one all-gather along the head axis, inside the
-timed region. The other BASELINE.json configs are measured as well and reported under
-"workloads" (each with its own roofline object); "--only NAME" restricts the run to one of them.
+Prints ONE JSON line. A "step" is one pass of the headline workload:
+
+* one GPU: the GQA prefill the 60 %-of-peak target is quoted on — causal bf16, B=2, Hq=32, Hkv=8,
+  S=8192, d=128 ("prefill_c3");
+* N > 1 GPUs (torchrun, one rank per GPU): the head-sharded shape — Hq=64, Hkv=8, d=128, B=1,
+  S=16384 ("prefill_c5"), total work fixed and split by KV-head groups over the ranks (strong
+  scaling); every rank ends with the full output: the all-gather is fused into the kernel's epilogue
+  (peer stores over NVLink) and sits inside the timed region.
+
+The other configurations are measured as well and reported, compactly, under "workloads" (each
+with its fraction of the measured and of the nominal peak); "--only NAME" restricts the run to one.
+At every N the run also checks, outside the timed region, what the timed calls produced
+("parity"): at N > 1 every rank recomputes, alone, the heads another rank owns and compares them
+bit for bit with what arrived in its gathered output; at N = 1 a slice is recomputed on the library's
+independent SIMT kernel.
 
 `--impl reference` times the CPU restatement of luma-cpu's math-path attention (oracle/) on the
-host cores: the reference's own implementation of this path is Rust and cannot be built with
-this image's toolchains.
+host cores, on the same workload definition: the reference's own implementation of this path is
+Rust and cannot be built with this image's toolchains.
 """
 from __future__ import annotations
 
@@ -33,13 +42,29 @@ sys.path.insert(0, str(ROOT))
 
 NOMINAL_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
+NOMINAL_NVLINK_GBS = 900.0
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from
-# the ncu captures summarised under profiles/. prefill_c2 was captured at full size; the decode
-# figure is the ratio measured on decode_c4_small (399.9 MB moved for 394.2 MB of algorithmic bytes,
-# L2 hit rate 0.4 %: traffic grows in proportion to the cached tokens) applied to the run's own bytes.
+# the ncu captures summarised under profiles/, as a ratio to the algorithmic bytes of the captured
+# case: the prefill captures are of prefill_c2 in full and of prefill_c3_small (B=1, 8 of 32 heads,
+# scaled to the full launch by the heads processed: traffic grows in proportion); the decode figure
+# is decode_c4_small (399.9 MB moved for 394.2 MB of algorithmic bytes, L2 hit rate 0.4 %).
 NCU_TRAFFIC_BYTES = {"prefill_c2": 512_585_728 + 51_621_632}
 NCU_DECODE_TRAFFIC_RATIO = (394_139_648 + 4_231_680) / 394_223_184
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# name -> (batch, q heads, kv heads, sequence, head size, seed, input scale, with LSE)
+PREFILL = {
+    "prefill_c2": (4, 32, 32, 2048, 128, 2, 1.0, True),
+    "prefill_c3": (2, 32, 8, 8192, 128, 3, 0.5, False),
+    "prefill_c3_small": (1, 8, 2, 8192, 128, 3, 0.5, False),     # same kernel and head layout, short ncu capture
+    "prefill_c5": (1, 64, 8, 16384, 128, 50, 1.0, False),
+}
+# name -> (sequences, q heads, kv heads, head size, page, shortest, longest context, pool pages, seed)
+DECODE = {
+    "decode_c4": (64, 32, 8, 128, 16, 512, 8192, 40000, 4),
+    "decode_c4_small": (16, 32, 8, 128, 16, 512, 8192, 12000, 4),  # 0.8 GB of cache: same kernel, short ncu capture
+    "decode_c5": (256, 64, 8, 128, 16, 1024, 32768, None, 51),
+}
 
 
 def load_peaks():
@@ -60,6 +85,38 @@ def causal_flops(b, hq, sq, skv, d, start_pos=0):
     i = np.arange(sq, dtype=np.int64)
     vis = np.minimum(skv, start_pos + i + 1).sum()
     return int(4 * d * b * hq * int(vis))
+
+
+def prefill_config(name, world=1):
+    b, hq, hkv, s, d, _seed, _sc, lse = PREFILL[name]
+    cfg = {"workload": name, "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d, "causal": True,
+           "lse": lse, "flops_per_step": causal_flops(b, hq, s, s, d), "l2": "inputs larger than L2"}
+    if world > 1:
+        cfg["parallelism"] = f"kv-head groups over {world} GPUs, fused all-gather of O"
+    return cfg
+
+
+# ------------------------------------------------------------------------------------------
+# host placement: keep a rank's pinned buffers and threads on the NUMA node of its GPU
+# ------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(torch, index):
+    """Restricts this process to the CPUs that are local to GPU `index` (from sysfs), so that pinned
+    staging buffers allocated afterwards come from that node. Returns the CPU list or None."""
+    try:
+        props = torch.cuda.get_device_properties(index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        text = Path(f"/sys/bus/pci/devices/{bus}/local_cpulist").read_text().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return text
+    except Exception:
+        pass
+    return None
 
 
 # ------------------------------------------------------------------------------------------
@@ -132,13 +189,11 @@ class ClockSampler:
         if sm:
             out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
                    "samples": len(sm)}
-            if step is not None:
-                out["note"] = "sampled from the start of the timed region through an untimed ~0.35 s repeat of the same step"
         return out
 
 
 # ------------------------------------------------------------------------------------------
-# workloads
+# inputs
 # ------------------------------------------------------------------------------------------
 def make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in=1.0):
     g = torch.Generator(device=dev)
@@ -149,7 +204,9 @@ def make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in=1.0):
     return q, k, v
 
 
-def make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool_pages, seed):
+def make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool_pages, seed, q_seed=None):
+    """Paged cache with a seeded permutation of physical pages; `q_seed` (default: seed) seeds the
+    query rows alone, so that ranks sharing a cache seed still ask different questions."""
     rng = np.random.Generator(np.random.Philox(seed))
     lens = rng.integers(lo, hi + 1, size=batch).astype(np.int32)
     need = (lens.astype(np.int64) + page - 1) // page
@@ -172,8 +229,14 @@ def make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool_pages, seed):
         n = min(step, pool_pages - i)
         kc[i:i + n] = torch.randn(n, page, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
         vc[i:i + n] = torch.randn(n, page, hkv, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    q = torch.randn(batch, 1, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q = make_decode_q(torch, dev, batch, hq, d, seed if q_seed is None else q_seed)
     return q, kc, vc, torch.from_numpy(lens).to(dev), torch.from_numpy(table).to(dev), lens
+
+
+def make_decode_q(torch, dev, batch, hq, d, q_seed):
+    g = torch.Generator(device=dev)
+    g.manual_seed(1_000_003 + q_seed)
+    return torch.randn(batch, 1, hq, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
 
 
 def decode_bytes(lens, hq, hkv, d, page):
@@ -200,7 +263,29 @@ def time_steps(torch, fn, steps, warmup, barrier=None):
     return e0.elapsed_time(e1) / 1e3  # seconds for K steps
 
 
-def run_prefill(torch, low, ffi, dev, name, b, hq, hkv, s, d, steps, warmup, peaks, seed, scale_in=1.0, want_lse=True):
+def _max_over_ranks(torch, dist, dev, sec):
+    if dist is None:
+        return sec
+    t = torch.tensor([sec], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def tensor_roofline(tf, peaks, traffic=None):
+    return {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+            "traffic": traffic, "peak_source": peaks["source"], "frac_nominal": tf / NOMINAL_TFLOPS}
+
+
+def hbm_roofline(gbs, peaks, traffic=None):
+    return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "traffic": traffic, "peak_source": peaks["source"], "frac_nominal": gbs / NOMINAL_HBM_GBS}
+
+
+# ------------------------------------------------------------------------------------------
+# single-GPU workloads
+# ------------------------------------------------------------------------------------------
+def run_prefill(torch, low, ffi, dev, name, steps, warmup, peaks):
+    b, hq, hkv, s, d, seed, scale_in, want_lse = PREFILL[name]
     q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in)
     o = torch.empty_like(q)
     lse = torch.empty(b, hq, s, device=dev, dtype=torch.float32) if want_lse else None
@@ -214,21 +299,41 @@ def run_prefill(torch, low, ffi, dev, name, b, hq, hkv, s, d, steps, warmup, pea
     sec = time_steps(torch, step, steps, warmup)
     flops = causal_flops(b, hq, s, s, d)
     tf = flops * steps / sec / 1e12
-    peak = peaks["bf16_tflops"]
-    res = {
-        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
-        "kernel_path": path, "launches_per_step": launches,
-        "config": {"workload": name, "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
-                   "causal": True, "lse": want_lse, "flops_per_step": flops,
-                   "l2_policy": "inputs larger than L2 (q+k+v+o = %d MiB)" % ((q.numel() * 2 + k.numel() * 4) * 2 // 2 ** 20 // 1)},
-        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
-                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
-                     "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
-    }
-    return res, (q, k, v, o, lse)
+    res = {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+           "kernel_path": path, "launches_per_step": launches, "config": prefill_config(name),
+           "roofline": tensor_roofline(tf, peaks, NCU_TRAFFIC_BYTES.get(name))}
+    return res, (q, k, v, o, lse), step
 
 
-def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool, steps, warmup, peaks, seed):
+def prefill_parity_single(torch, low, ffi, q, k, v, o):
+    """One GPU: the timed kernel's output for one KV-head group of the last batch element, rows
+    [0, 1024), against the library's SIMT tile kernel (f32 scalar arithmetic, no tensor cores, no TMA)
+    on the same inputs. Untimed."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    group = hq // hkv
+    rows = min(s, 1024)
+    kvh = hkv - 1
+    qs = q[b - 1:b, :rows, kvh * group:(kvh + 1) * group].contiguous()
+    ks = k[b - 1:b, :rows, kvh:kvh + 1].contiguous()
+    vs = v[b - 1:b, :rows, kvh:kvh + 1].contiguous()
+    ref = torch.empty_like(qs)
+    ffi.set_option("force_generic", 1)
+    try:
+        low.flash_attn(qs, ks, vs, ref, 1, rows, rows, group, 1, d, 0, 1.0 / math.sqrt(d))
+        path = ffi.last_path()
+    finally:
+        ffi.set_option("force_generic", 0)
+    torch.cuda.synchronize()
+    got = o[b - 1:b, :rows, kvh * group:(kvh + 1) * group].float()
+    err = (got - ref.float()).abs()
+    ok = bool(torch.isfinite(got).all()) and float(err.max()) <= 2e-2 and float(err.mean()) <= 2e-3 and path == "tile_simt"
+    return {"checked_ranks": 1, "ok": ok, "against": "tile_simt kernel, one KV-head group, 1024 rows",
+            "max_abs_err": float(err.max())}
+
+
+def run_decode(torch, low, ffi, dev, name, steps, warmup, peaks):
+    batch, hq, hkv, d, page, lo, hi, pool, seed = DECODE[name]
     q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool, seed)
     o = torch.empty_like(q)
     scale = 1.0 / math.sqrt(d)
@@ -242,19 +347,13 @@ def run_decode(torch, low, ffi, dev, name, batch, hq, hkv, d, page, lo, hi, pool
     sec = time_steps(torch, step, steps, warmup)
     nbytes = decode_bytes(lens, hq, hkv, d, page)
     gbs = nbytes * steps / sec / 1e9
-    peak = peaks["hbm_gbs"]
-    res = {
-        "metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
-        "kernel_path": path, "launches_per_step": launches,
-        "config": {"workload": name, "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "page_size": page,
-                   "context": [int(lo), int(hi)], "tokens": int(lens.sum()), "pool_pages": int(kc.shape[0]),
-                   "bytes_per_step": nbytes, "l2_policy": "K/V touched per step (%d MiB) larger than L2" % (nbytes // 2 ** 20)},
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                     "traffic": int(nbytes * NCU_DECODE_TRAFFIC_RATIO),
-                     "peak_source": f"of {peaks['source']} (copy bandwidth)",
-                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS},
-    }
-    return res, (q, kc, vc, o, lens_d, table_d)
+    res = {"metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
+           "kernel_path": path, "launches_per_step": launches,
+           "config": {"workload": name, "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d, "page_size": page,
+                      "context": [int(lo), int(hi)], "tokens": int(lens.sum()), "pool_pages": int(kc.shape[0]),
+                      "bytes_per_step": nbytes, "l2": "K/V touched per step larger than L2"},
+           "roofline": hbm_roofline(gbs, peaks, int(nbytes * NCU_DECODE_TRAFFIC_RATIO))}
+    return res
 
 
 def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, lo, hi, steps, warmup, peaks, seed):
@@ -276,15 +375,11 @@ def run_paged_prefill(torch, low, ffi, dev, name, batch, sq, hq, hkv, d, page, l
     sec = time_steps(torch, step, steps, warmup)
     flops = sum(causal_flops(1, hq, sq, int(L), d, int(L) - sq) for L in lens)
     tf = flops * steps / sec / 1e12
-    peak = peaks["bf16_tflops"]
-    return {
-        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
-        "kernel_path": path, "launches_per_step": launches,
-        "config": {"workload": name, "batch": batch, "chunk": sq, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
-                   "page_size": page, "context": [int(lo), int(hi)], "flops_per_step": flops},
-        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
-                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)", "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
-    }
+    return {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+            "kernel_path": path, "launches_per_step": launches,
+            "config": {"workload": name, "batch": batch, "chunk": sq, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+                       "page_size": page, "context": [int(lo), int(hi)], "flops_per_step": flops},
+            "roofline": tensor_roofline(tf, peaks)}
 
 
 def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d, steps, warmup, peaks, seed):
@@ -312,16 +407,11 @@ def run_varlen_prefill(torch, low, ffi, dev, name, num_seqs, lo, hi, hq, hkv, d,
     sec = time_steps(torch, step, steps, warmup)
     flops = sum(causal_flops(1, hq, int(L), int(L), d) for L in lens)
     tf = flops * steps / sec / 1e12
-    peak = peaks["bf16_tflops"]
-    return {
-        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
-        "kernel_path": path, "launches_per_step": launches,
-        "config": {"workload": name, "num_seqs": num_seqs, "prompt_tokens": [int(lo), int(hi)], "total_tokens": total,
-                   "q_heads": hq, "kv_heads": hkv, "head_dim": d, "flops_per_step": flops,
-                   "l2_policy": "inputs larger than L2"},
-        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
-                     "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)", "frac_of_nominal_2250": tf / NOMINAL_TFLOPS},
-    }
+    return {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / steps * 1e3,
+            "kernel_path": path, "launches_per_step": launches,
+            "config": {"workload": name, "num_seqs": num_seqs, "prompt_tokens": [int(lo), int(hi)], "total_tokens": total,
+                       "q_heads": hq, "kv_heads": hkv, "head_dim": d, "flops_per_step": flops},
+            "roofline": tensor_roofline(tf, peaks)}
 
 
 def run_softmax(torch, low, ffi, dev, name, rows, n, dtype_name, steps, warmup, peaks, seed):
@@ -340,194 +430,330 @@ def run_softmax(torch, low, ffi, dev, name, rows, n, dtype_name, steps, warmup, 
     sec = time_steps(torch, step, steps, warmup)
     nbytes = 2 * rows * n * x.element_size()
     gbs = nbytes * steps / sec / 1e9
-    return {
-        "metric": "row-softmax HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
-        "kernel_path": path, "launches_per_step": launches,
-        "config": {"workload": name, "rows": rows, "row_size": n, "dtype": dtype_name, "bytes_per_step": nbytes,
-                   "l2_policy": "inputs larger than L2"},
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth)",
-                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS},
-    }
+    return {"metric": "row-softmax HBM GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": sec / steps * 1e3,
+            "kernel_path": path, "launches_per_step": launches,
+            "config": {"workload": name, "rows": rows, "row_size": n, "dtype": dtype_name, "bytes_per_step": nbytes},
+            "roofline": hbm_roofline(gbs, peaks)}
 
 
-NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction on this pool (nominal 900)
+# ------------------------------------------------------------------------------------------
+# head-sharded workloads (strong scaling over the ranks; run at every N, N = 1 included)
+# ------------------------------------------------------------------------------------------
+def measure_peer_copy_gbs(torch, ffi, dist, dev, peer, rank, world, nbytes):
+    """Peer bandwidth of this very run: every rank copies `nbytes` from its own memory into the
+    next rank's shared output buffer (one cudaMemcpyAsync, all ranks at once, CUDA events, best of
+    three); the slowest rank's figure is returned."""
+    src = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    src.zero_()
+    dst = peer.ptrs[(rank + 1) % world]
+    st = torch.cuda.current_stream(dev).cuda_stream
+    best = float("inf")
+    for it in range(4):
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if ffi.lib.luma_peer_copy(dst, src.data_ptr(), nbytes, st) != 0:
+            raise RuntimeError(ffi.lib.luma_comm_last_error().decode())
+        e1.record()
+        torch.cuda.synchronize()
+        if it > 0:
+            best = min(best, e0.elapsed_time(e1) / 1e3)
+    t = torch.tensor([best], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    return nbytes / float(t.item()) / 1e9
 
 
-def fused_roofline(flops_per_gpu, nvlink_out_bytes_per_gpu, sec_per_step, peaks):
+def fused_roofline(flops_per_gpu, nvlink_out_bytes_per_gpu, sec_per_step, peaks, peer_gbs):
     """Roofline of the fused attention + all-gather kernel, per GPU: the target time is the slower of
-    FLOPs / measured GEMM peak and bytes stored to peers over NVLink / measured peer bandwidth."""
+    FLOPs / measured GEMM peak and bytes stored to peers over NVLink / the peer bandwidth measured in
+    this run."""
     t_math = flops_per_gpu / (peaks["bf16_tflops"] * 1e12)
-    t_link = nvlink_out_bytes_per_gpu / (NVLINK_PEER_GBS * 1e9)
+    t_link = nvlink_out_bytes_per_gpu / (peer_gbs * 1e9) if peer_gbs else 0.0
     if t_link > t_math:
         gbs = nvlink_out_bytes_per_gpu / sec_per_step / 1e9
-        return {"bound": "nvlink", "achieved": gbs, "peak": NVLINK_PEER_GBS, "unit": "GB/s", "frac": gbs / NVLINK_PEER_GBS,
-                "traffic": None, "peak_source": "measured peer copy, per direction per GPU; bytes = this GPU's O shard "
-                                                "stored to every peer", "target_ms": t_link * 1e3}
+        return {"bound": "nvlink", "achieved": gbs, "peak": peer_gbs, "unit": "GB/s", "frac": gbs / peer_gbs, "traffic": None,
+                "peak_source": "peer copy measured in this run", "frac_nominal": gbs / NOMINAL_NVLINK_GBS,
+                "target_ms": t_link * 1e3}
     tf = flops_per_gpu / sec_per_step / 1e12
-    return {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-            "frac": tf / peaks["bf16_tflops"], "traffic": None,
-            "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst); per GPU, all-gather included",
-            "frac_of_nominal_2250": tf / NOMINAL_TFLOPS, "target_ms": t_math * 1e3}
+    r = tensor_roofline(tf, peaks)
+    r["target_ms"] = t_math * 1e3
+    return r
 
 
-def _max_over_ranks(torch, dist, dev, sec):
-    if dist is None:
-        return sec
-    t = torch.tensor([sec], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, b, hq, hkv, s, d, steps, warmup, peaks, seed, chunks=4):
+def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, warmup, peaks, sampler=None):
     """Strong scaling: the (b, s, hq, d) problem is split by KV-head groups over `world` ranks; every
-    rank ends with the full O (the kernel stores its heads into every rank's output buffer)."""
+    rank ends with the full O (the kernel stores its heads into every rank's output buffer). Rank r's
+    inputs come from seed + r, so any rank can regenerate any other rank's shard for the parity check."""
     from luma_b200 import dist as fdist
+    b, hq, hkv, s, d, seed, scale_in, _lse = PREFILL[name]
     qs, kvs = fdist.shard_heads(hq, hkv, world, rank)
     hq_l, hkv_l = qs.stop - qs.start, kvs.stop - kvs.start
-    q, k, v = make_prefill(torch, dev, b, hq_l, hkv_l, s, d, seed + rank)
+    q, k, v = make_prefill(torch, dev, b, hq_l, hkv_l, s, d, seed + rank, scale_in)
     scale = 1.0 / math.sqrt(d)
     launches = [0]
+    peer_gbs = None
     if world > 1:
         peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
+        peer_gbs = measure_peer_copy_gbs(torch, ffi, dist, dev, peer, rank, world, min(256 << 20, peer.out.numel() * 2))
+        out = peer.out
 
         def step():
             peer.fused_attention(q, k, v, hq, qs.start, scale=scale)
             peer.sync()
             launches[0] = 2
     else:
-        o_local = torch.empty_like(q)
+        out = torch.empty_like(q)
 
         def step():
-            low.flash_attn(q, k, v, o_local, b, s, s, hq_l, hkv_l, d, 0, scale)
+            low.flash_attn(q, k, v, out, b, s, s, hq_l, hkv_l, d, 0, scale)
             launches[0] = ffi.last_launches()
 
     step()
     path = ffi.last_path()
     barrier = (lambda: dist.barrier()) if dist is not None else None
+    if sampler is not None:
+        sampler.start()
     sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, barrier))
+    clocks = sampler.stop(torch, step, barrier, repeats=(0.35 / max(sec / steps, 1e-6)) if world > 1 else None) if sampler is not None else None
+
+    # ---- parity, untimed: what is in `out` after the timed steps -------------------------------
     if world > 1:
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        other = (rank + 1) % world
+        oq, okv = fdist.shard_heads(hq, hkv, world, other)
+        q2, k2, v2 = make_prefill(torch, dev, b, hq_l, hkv_l, s, d, seed + other, scale_in)
+        ref = torch.empty_like(q2)
+        low.flash_attn(q2, k2, v2, ref, b, s, s, hq_l, hkv_l, d, 0, scale)
+        torch.cuda.synchronize()
+        ok = bool(torch.equal(out[:, :, oq], ref)) and bool(torch.isfinite(out.float()).all())
+        mine = torch.empty_like(q)
+        low.flash_attn(q, k, v, mine, b, s, s, hq_l, hkv_l, d, 0, scale)
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.equal(out[:, :, qs], mine))
+        t = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        parity = {"checked_ranks": world, "ok": bool(t.item() == 1.0),
+                  "against": "every rank recomputes the next rank's heads and its own alone; bit-exact with the gathered output"}
+        del q2, k2, v2, ref, mine
         peer.close()
+    else:
+        parity = prefill_parity_single(torch, low, ffi, q, k, v, out)
     flops = causal_flops(b, hq, s, s, d)
     tf = flops * steps / sec / 1e12
-    peak = peaks["bf16_tflops"]
-    return {
-        "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "per_gpu": tf / world,
-        "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
-        "launches_per_step": launches[0],
-        "config": {"workload": "prefill_c5", "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
-                   "causal": True, "flops_per_step": flops,
-                   "parallelism": f"KV-head groups over {world} GPU(s); all-gather of O fused into the kernel epilogue "
-                                  "(peer stores over NVLink) + one 4-byte all-reduce"},
-        "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks),
-    }
+    res = {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "per_gpu": tf / world,
+           "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
+           "launches_per_step": launches[0], "config": prefill_config(name, world), "parity": parity,
+           "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks, peer_gbs) if world > 1
+           else tensor_roofline(tf, peaks)}
+    if peer_gbs is not None:
+        res["peer_copy_gbs"] = peer_gbs
+    return res, clocks, (q, k, v)
 
 
-def run_sharded_decode(torch, low, ffi, dev, dist, world, rank, batch, hq, hkv, d, page, lo, hi, steps, warmup, peaks, seed):
+def run_sharded_decode(torch, low, ffi, dev, dist, world, rank, name, steps, warmup, peaks):
     """Strong scaling of paged decode: every rank holds the cache slice of its KV heads
-    (num_blocks, page, hkv/world, d); block tables and lengths are replicated; O is all-gathered."""
+    (num_blocks, page, hkv/world, d); block tables and lengths are replicated; the merge kernel stores
+    its heads into every rank's (batch, 1, hq, d) output. All ranks build their cache slice from the
+    same seed and differ in their query rows, so a rank can recompute another rank's heads alone."""
     from luma_b200 import dist as fdist
+    batch, hq, hkv, d, page, lo, hi, pool, seed = DECODE[name]
     qs, kvs = fdist.shard_heads(hq, hkv, world, rank)
     hq_l, hkv_l = qs.stop - qs.start, kvs.stop - kvs.start
-    q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq_l, hkv_l, d, page, lo, hi, None, seed)
-    o_local = torch.empty_like(q)
+    q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq_l, hkv_l, d, page, lo, hi, pool, seed, q_seed=seed + rank)
     scale = 1.0 / math.sqrt(d)
     max_blocks = table_d.shape[1]
-    gather = fdist.HeadAllGather(dist.group.WORLD, (batch, 1, hq_l, d), torch.bfloat16, dev) if world > 1 else None
+    if world > 1:
+        peer = fdist.PeerOutput(dist.group.WORLD, (batch, 1, hq, d), torch.bfloat16, dev)
+        out = peer.out
 
-    def step():
-        low.flash_attn_with_kvcache(q, kc, vc, o_local, table_d, lens_d, batch, 1, hq_l, hkv_l, d, page, max_blocks, scale)
-        if gather is not None:
-            gather(o_local)
+        def step():
+            peer.fused_decode(q, kc, vc, table_d, lens_d, hq, qs.start, scale)
+            peer.sync()
+    else:
+        out = torch.empty_like(q)
+
+        def step():
+            low.flash_attn_with_kvcache(q, kc, vc, out, table_d, lens_d, batch, 1, hq_l, hkv_l, d, page, max_blocks, scale)
 
     step()
-    path, launches = ffi.last_path(), ffi.last_launches() + (2 if gather is not None else 0)
+    path, launches = ffi.last_path(), ffi.last_launches() + (1 if world > 1 else 0)
     barrier = (lambda: dist.barrier()) if dist is not None else None
     sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, barrier))
+    parity = None
+    if world > 1:
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        other = (rank + 1) % world
+        oq, _ = fdist.shard_heads(hq, hkv, world, other)
+        q2 = make_decode_q(torch, dev, batch, hq_l, d, seed + other)
+        ref = torch.empty_like(q2)
+        low.flash_attn_with_kvcache(q2, kc, vc, ref, table_d, lens_d, batch, 1, hq_l, hkv_l, d, page, max_blocks, scale)
+        torch.cuda.synchronize()
+        ok = bool(torch.equal(out[:, :, oq], ref)) and bool(torch.isfinite(out.float()).all())
+        t = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        parity = {"checked_ranks": world, "ok": bool(t.item() == 1.0)}
+        peer.close()
     nbytes = decode_bytes(lens, hq, hkv, d, page)   # whole job: all KV heads
     gbs = nbytes * steps / sec / 1e9
-    peak = peaks["hbm_gbs"]
-    return {
-        "metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "per_gpu": gbs / world,
-        "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
-        "launches_per_step": launches,
-        "config": {"workload": "decode_c5", "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
-                   "page_size": page, "context": [int(lo), int(hi)], "tokens": int(lens.sum()),
-                   "pool_pages": int(kc.shape[0]), "bytes_per_step": nbytes,
-                   "parallelism": f"KV heads over {world} GPU(s), all-gather of O"},
-        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
-                     "traffic": None, "peak_source": f"of {peaks['source']} (copy bandwidth); per GPU, all-gather included",
-                     "frac_of_nominal_8000": gbs / world / NOMINAL_HBM_GBS},
-    }
+    r = hbm_roofline(gbs / world, peaks)
+    return {"metric": "paged-decode HBM GB/s", "value": gbs, "unit": "GB/s", "per_gpu": gbs / world,
+            "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
+            "launches_per_step": launches, "parity": parity,
+            "config": {"workload": name, "batch": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+                       "page_size": page, "context": [int(lo), int(hi)], "tokens": int(lens.sum()),
+                       "pool_pages": int(kc.shape[0]), "bytes_per_step": nbytes},
+            "roofline": r}
+
+
+def run_weak_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, warmup, peaks):
+    """Weak scaling: every rank owns the heads of one whole `name` problem of a world-times-wider layer
+    and stores them into every rank's output (NVLink-bound by construction at larger N)."""
+    from luma_b200 import dist as fdist
+    b, hq, hkv, s, d, seed, scale_in, _lse = PREFILL[name]
+    q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed + rank, scale_in)
+    peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq * world, d), torch.bfloat16, dev)
+
+    def step():
+        peer.fused_attention(q, k, v, hq * world, hq * rank)
+        peer.sync()
+
+    step()
+    sec = _max_over_ranks(torch, dist, dev, time_steps(torch, step, steps, warmup, lambda: dist.barrier()))
+    peer.close()
+    flops = causal_flops(b, hq, s, s, d) * world
+    tf = flops * steps / sec / 1e12
+    return {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "per_gpu": tf / world, "ms_per_step": sec / steps * 1e3,
+            "scaling": "weak", "n_gpus": world, "config": {"workload": name + "_weak", "q_heads": hq * world},
+            "roofline": {"bound": "nvlink", "achieved": q.numel() * 2 * (world - 1) / (sec / steps) / 1e9, "unit": "GB/s"}}
 
 
 # ------------------------------------------------------------------------------------------
-# CPU baseline (oracle port of luma-cpu's math path) — bounded sample of the primary workload
+# end to end through the host-tensor API
 # ------------------------------------------------------------------------------------------
-def cpu_baseline_prefill(b, hq, hkv, s, d, budget_s=12.0, seed=0):
+def run_e2e(torch, dev, dist, q, k, v, flops_total, steps):
+    """Same metric through luma_b200.high.flash_attn_func_host: this rank's q/k/v in pinned HOST
+    memory -> device, kernel, output -> pinned host, every step. Max over ranks."""
+    from luma_b200 import high
+    hq_h, hk_h, hv_h = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        high.flash_attn_func_host(hq_h, hk_h, hv_h, ho, None, True, 0, dev)
+
+    barrier = (lambda: dist.barrier()) if dist is not None else None
+    sec = _max_over_ranks(torch, dist, dev, time_steps(torch, e2e_step, steps, 2, barrier))
+    ok = bool(torch.isfinite(ho.float()).all())
+    return {"value": flops_total * steps / sec / 1e12, "unit": "TFLOP/s",
+            "h2d_bytes_per_step": int((q.numel() + k.numel() + v.numel()) * 2), "d2h_bytes_per_step": int(q.numel() * 2),
+            "steps": steps, "ms_per_step": sec / steps * 1e3, "finite": ok,
+            "api": "high.flash_attn_func_host (pinned host in/out, row chunks pipelined over 3 streams); bytes per GPU"}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline (oracle port of luma-cpu's math path) — bounded sample of the headline workload
+# ------------------------------------------------------------------------------------------
+def cpu_sample_inputs(name, n_heads, seed=0):
+    """One batch element, one KV head and `n_heads` of its query heads, full sequence length."""
+    _b, _hq, _hkv, s, d, _seed, scale_in, _lse = PREFILL[name]
+    rng = np.random.Generator(np.random.Philox(seed))
+    q = rng.standard_normal((1, s, n_heads, d), dtype=np.float32) * np.float32(scale_in)
+    k = rng.standard_normal((1, s, 1, d), dtype=np.float32) * np.float32(scale_in)
+    v = rng.standard_normal((1, s, 1, d), dtype=np.float32) * np.float32(scale_in)
+    return q, k, v
+
+
+def cpu_sample_text(name, n_heads):
+    b, hq, hkv, s, _d, _seed, _sc, _lse = PREFILL[name]
+    return (f"1 of {b} batch elements x 1 of {hkv} KV heads x {n_heads} of its {hq // hkv} query heads, full S={s}; "
+            "f32 math path over the full key range (oracle port of luma-cpu); rate counts causal FLOPs only")
+
+
+def cpu_baseline_prefill(name, budget_s=12.0):
     from oracle import binding as ob
     cores = ob.hardware_threads()
+    _b, hq, hkv, s, d, _seed, _sc, _lse = PREFILL[name]
     group = hq // hkv
-    rng = np.random.Generator(np.random.Philox(seed))
-
-    def make(nh_kv):
-        q = rng.standard_normal((1, s, nh_kv * group, d), dtype=np.float32)
-        k = rng.standard_normal((1, s, nh_kv, d), dtype=np.float32)
-        v = rng.standard_normal((1, s, nh_kv, d), dtype=np.float32)
-        return q, k, v
-
-    # probe with one KV head (and its query heads) of one batch element
-    q, k, v = make(1)
+    q, k, v = cpu_sample_inputs(name, 1)
     t0 = time.perf_counter()
     ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
     probe = time.perf_counter() - t0
-    nh = int(max(1, min(hkv, budget_s / max(probe, 1e-3))))
+    nh = int(max(1, min(group, budget_s / max(probe, 1e-3))))
     if nh > 1:
-        q, k, v = make(nh)
+        q, k, v = cpu_sample_inputs(name, nh)
         t0 = time.perf_counter()
         ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
         sec = time.perf_counter() - t0
     else:
         sec = probe
-    flops = causal_flops(1, nh * group, s, s, d)
+    flops = causal_flops(1, nh, s, s, d)
     return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"1 of {b} batch elements x {nh * group} of {hq} query heads ({nh} KV heads), full S={s}, "
-                      f"f32 math path over the full key range, {sec:.2f} s; rate counts causal FLOPs only"}, sec
+            "sample": cpu_sample_text(name, nh) + f"; {sec:.2f} s"}
 
 
 def reference_arm(args):
-    """`--impl reference`: the CPU path, timed per step on a bounded sample of the primary workload."""
+    """`--impl reference`: the CPU path on the host cores, K timed steps after W warm-up steps as
+    given, each step a bounded sample of the same headline workload as the GPU arm at this N."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    b, hq, hkv, s, d = 4, 32, 32, 2048, 128
+    world = max(1, int(os.environ.get("WORLD_SIZE", str(args.gpus))))
+    name = "prefill_c3" if world == 1 else "prefill_c5"
     from oracle import binding as ob
     cores = ob.hardware_threads()
-    rng = np.random.Generator(np.random.Philox(0))
-    nh = 2
-    q = rng.standard_normal((1, s, nh, d), dtype=np.float32)
-    k = rng.standard_normal((1, s, nh, d), dtype=np.float32)
-    v = rng.standard_normal((1, s, nh, d), dtype=np.float32)
-    for _ in range(min(args.warmup, 2)):
+    _b, hq, hkv, s, d, _seed, _sc, _lse = PREFILL[name]
+    group = hq // hkv
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    # size the sample so that the whole run stays within about two and a half minutes
+    q, k, v = cpu_sample_inputs(name, 1)
+    t0 = time.perf_counter()
+    ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
+    probe = time.perf_counter() - t0
+    nh = int(max(1, min(group, 150.0 / max(probe * (steps + warmup), 1e-3))))
+    if nh > 1:
+        q, k, v = cpu_sample_inputs(name, nh)
+    for _ in range(warmup):
         ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
         ob.sdpa_math_f32(q, k, v, causal=True, nthreads=cores)
     sec = time.perf_counter() - t0
     flops = causal_flops(1, nh, s, s, d)
     tf = flops * steps / sec / 1e12
-    sample = f"1 of {b} batch elements x {nh} of {hq} heads per step, full S={s}; f32 math path (oracle port of luma-cpu)"
     print(json.dumps({
         "impl": "reference", "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": sec / steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "prefill_c2", "batch": b, "q_heads": hq, "kv_heads": hkv, "seq_len": s, "head_dim": d,
-                   "causal": True},
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": sec / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": prefill_config(name, world),
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": cpu_sample_text(name, nh)},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def compact(res):
+    """A workload's entry under "workloads": the figures, not the prose."""
+    out = {"value": round(res["value"], 1), "unit": res["unit"], "ms": round(res["ms_per_step"], 4),
+           "frac": round(res["roofline"].get("frac", 0.0), 4) if res["roofline"].get("frac") is not None else None,
+           "frac_nominal": round(res["roofline"]["frac_nominal"], 4) if res["roofline"].get("frac_nominal") is not None else None,
+           "bound": res["roofline"]["bound"]}
+    for key in ("per_gpu", "scaling", "peer_copy_gbs"):
+        if key in res:
+            out[key] = round(res[key], 1) if isinstance(res[key], float) else res[key]
+    if res.get("parity") is not None:
+        out["parity_ok"] = res["parity"]["ok"]
+    return out
 
 
 # ------------------------------------------------------------------------------------------
@@ -537,18 +763,18 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, help="run just one workload: prefill_c2, prefill_c3, decode_c4, prefill_c5, decode_c5")
+    ap.add_argument("--only", default=None, help="headline plus just one other workload: prefill_c2, decode_c4, paged_prefill, "
+                                                  "varlen_prefill, softmax_scores, prefill_c5, decode_c5, none")
     ap.add_argument("--profile", default=None,
-                    help="run ONE workload and nothing else (for ncu): prefill_c2, prefill_c3, prefill_c3_small, "
-                         "decode_c4, decode_c4_small, decode_c5")
+                    help="run ONE workload and nothing else (for ncu): prefill_c2, prefill_c3, prefill_c3_small, prefill_c5, "
+                         "decode_c4, decode_c4_small, decode_c5, varlen_prefill, softmax_<dtype>_<rows>x<row_size>")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--small", action="store_true", help="shrink every workload (for profiler captures)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small and not args.profile else args.warmup
 
     if args.impl == "reference":
         reference_arm(args)
         return
+    args.warmup = max(args.warmup, 3) if not args.profile else args.warmup
 
     import torch
     from luma_b200 import ffi, low
@@ -559,6 +785,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the measured path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = bind_to_gpu_numa_node(torch, local_rank)
     peaks = load_peaks()
     dist = None
     if world > 1:
@@ -566,36 +793,19 @@ def main():
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-
     if args.profile:
         # one workload, nothing else: the command line the ncu summaries under profiles/ were made with
         name = args.profile
-        if name == "prefill_c2":
-            res, _ = run_prefill(torch, low, ffi, dev, name, 4, 32, 32, 2048, 128, args.steps, args.warmup, peaks, seed=2)
-        elif name == "prefill_c3":
-            res, _ = run_prefill(torch, low, ffi, dev, name, 2, 32, 8, 8192, 128, args.steps, args.warmup, peaks, seed=3,
-                                 scale_in=0.5, want_lse=False)
-        elif name == "prefill_c3_small":   # one batch element, 8 of 32 heads: same kernel, short capture
-            res, _ = run_prefill(torch, low, ffi, dev, name, 1, 8, 2, 8192, 128, args.steps, args.warmup, peaks, seed=3,
-                                 scale_in=0.5, want_lse=False)
+        if name in PREFILL:
+            res, _bufs, _step = run_prefill(torch, low, ffi, dev, name, args.steps, args.warmup, peaks)
+        elif name in DECODE:
+            res = run_decode(torch, low, ffi, dev, name, args.steps, args.warmup, peaks)
         elif name == "varlen_prefill":
             res = run_varlen_prefill(torch, low, ffi, dev, name, 32, 1024, 8192, 32, 8, 128, args.steps, args.warmup, peaks, seed=7)
         elif name.startswith("softmax_"):   # softmax_<dtype>_<rows>x<row_size>, e.g. softmax_bf16_131072x4096
             _, dtn, shp = name.split("_")
             r_, n_ = (int(t) for t in shp.split("x"))
             res = run_softmax(torch, low, ffi, dev, name, r_, n_, dtn, args.steps, args.warmup, peaks, seed=8)
-        elif name == "decode_c4":
-            res, _ = run_decode(torch, low, ffi, dev, name, 64, 32, 8, 128, 16, 512, 8192, 40000, args.steps, args.warmup,
-                                peaks, seed=4)
-        elif name == "decode_c4_small":    # 16 sequences, 12k-page pool (0.8 GB of cache): same kernel
-            res, _ = run_decode(torch, low, ffi, dev, name, 16, 32, 8, 128, 16, 512, 8192, 12000, args.steps, args.warmup,
-                                peaks, seed=4)
-        elif name == "decode_c5":
-            res, _ = run_decode(torch, low, ffi, dev, name, 256, 64, 8, 128, 16, 1024, 32768, None, args.steps, args.warmup,
-                                peaks, seed=5)
         else:
             raise SystemExit(f"unknown --profile {name}")
         print(json.dumps(res))
@@ -605,138 +815,98 @@ def main():
     workloads = {}
     only = args.only
     K, W = args.steps, args.warmup
+    extra_steps = max(3, min(K, 10))
 
-    # ---- primary: BASELINE.json configs[1] --------------------------------------------------
-    b, hq, hkv, s, d = (4, 32, 32, 2048, 128) if not args.small else (1, 8, 8, 2048, 128)
+    # ---- headline ---------------------------------------------------------------------------
     if world == 1:
         sampler.start()
-        primary, bufs = run_prefill(torch, low, ffi, dev, "prefill_c2", b, hq, hkv, s, d, K, W, peaks, seed=2)
-        q, k, v, o, lse = bufs
-        clocks = sampler.stop(torch, lambda: low.flash_attn(q, k, v, o, b, s, s, hq, hkv, d, 0, 1.0 / math.sqrt(d), None, None, lse))
-        scaling_note = "single GPU"
+        primary, bufs, step = run_prefill(torch, low, ffi, dev, "prefill_c3", K, W, peaks)
+        clocks = sampler.stop(torch, step)
+        q, k, v, o, _lse = bufs
+        primary["parity"] = prefill_parity_single(torch, low, ffi, q, k, v, o)
+        primary["scaling"] = "weak"
+        del o, bufs, step
     else:
-        from luma_b200 import dist as fdist
-        q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed=2 + rank)
-        lse = torch.empty(b, hq, s, device=dev, dtype=torch.float32)
-        # the kernel's epilogue stores this rank's heads into every rank's full output (peer memory
-        # over NVLink); one tiny all-reduce then tells everyone that all stores have landed
-        peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq * world, d), torch.bfloat16, dev)
-        o_local = peer.out
-
-        def step():
-            peer.fused_attention(q, k, v, hq * world, hq * rank, lse=lse)
-            peer.sync()
-
-        step()
-        path, launches = ffi.last_path(), ffi.last_launches() + 1
-        sampler.start()
-        sec = time_steps(torch, step, K, W, barrier)
-        t = torch.tensor([sec], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-        clocks = sampler.stop(torch, step, barrier, repeats=0.35 / max(sec / K, 1e-6))
-        flops = causal_flops(b, hq, s, s, d) * world
-        tf = flops * K / sec / 1e12
-        primary = {
-            "metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec / K * 1e3,
-            "kernel_path": path, "launches_per_step": launches,
-            "config": {"workload": "prefill_c2", "batch": b, "q_heads": hq * world, "kv_heads": hkv * world,
-                       "seq_len": s, "head_dim": d, "causal": True, "lse": True, "flops_per_step": flops,
-                       "parallelism": f"head-sharded x{world} (32 heads per GPU); the all-gather of O along heads is fused "
-                                      "into the kernel epilogue (peer stores over NVLink) + one 4-byte all-reduce",
-                       "l2_policy": "inputs larger than L2"},
-            "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / K, peaks),
-        }
-        o = o_local
-        scaling_note = "weak: 32 heads per GPU"
+        primary, clocks, (q, k, v) = run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, "prefill_c5", K, W, peaks, sampler)
 
     # ---- end to end through the host API with HOST buffers ------------------------------------
-    from luma_b200 import high
-    hq_h, hk_h, hv_h = (t.cpu().pin_memory() for t in (q, k, v))
-    ho = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
-
-    def e2e_step():
-        # the library's host-tensor call: batch elements pipelined over copy-in / kernel / copy-out streams
-        high.flash_attn_func_host(hq_h, hk_h, hv_h, ho, None, True, 0, dev)
-
-    e2e_steps = max(3, min(K, 10))
-    sec_e2e = time_steps(torch, e2e_step, e2e_steps, 2, barrier)
-    if dist is not None:
-        t = torch.tensor([sec_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec_e2e = float(t.item())
-    e2e_flops = causal_flops(b, hq, s, s, d) * world
-    e2e = {"value": e2e_flops * e2e_steps / sec_e2e / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": int((q.numel() + k.numel() + v.numel()) * 2),
-           "d2h_bytes_per_step": int(q.numel() * 2), "steps": e2e_steps,
-           "note": "luma_b200.high.flash_attn_func_host: pinned host q/k/v -> device, kernel, output -> pinned host, one batch "
-                   "element at a time over three streams (both directions of the host link busy), per step, per GPU"}
-    del hq_h, hk_h, hv_h, ho
-
-    # ---- the other BASELINE.json configs ------------------------------------------------------
-    if world > 1:
-        peer.close()
-    del q, k, v, o, lse
+    e2e = run_e2e(torch, dev, dist, q, k, v, primary["config"]["flops_per_step"], max(3, min(K, 10)))
+    del q, k, v
     torch.cuda.empty_cache()
-    if world == 1 and not args.small:
-        extra_steps = max(3, min(K, 10))
-        if only in (None, "prefill_c3"):
-            workloads["prefill_c3"], _b = run_prefill(torch, low, ffi, dev, "prefill_c3", 2, 32, 8, 8192, 128,
-                                                      extra_steps, 3, peaks, seed=3, scale_in=0.5, want_lse=False)
-            del _b
-            torch.cuda.empty_cache()
-        if only in (None, "paged_prefill"):
-            # the step before decode (not a BASELINE config): 1024-token chunks over paged contexts
-            workloads["paged_prefill"] = run_paged_prefill(torch, low, ffi, dev, "paged_prefill", 16, 1024, 32, 8, 128, 16,
-                                                           1024, 8192, extra_steps, 3, peaks, seed=6)
-            torch.cuda.empty_cache()
-        if only in (None, "varlen_prefill"):
-            # not a BASELINE config: 32 prompts of 1024..8192 tokens packed, GQA 32/8 (q+k+v+o = 230 MB at the mean)
-            workloads["varlen_prefill"] = run_varlen_prefill(torch, low, ffi, dev, "varlen_prefill", 32, 1024, 8192, 32, 8, 128,
-                                                             extra_steps, 3, peaks, seed=7)
-            torch.cuda.empty_cache()
-        if only in (None, "softmax_scores"):
-            # not a BASELINE config: the scores of one configs[2]-sized head group on the math path, bf16
-            workloads["softmax_scores"] = run_softmax(torch, low, ffi, dev, "softmax_scores", 131072, 4096, "bf16",
-                                                      extra_steps, 3, peaks, seed=8)
+
+    # ---- the other configurations -----------------------------------------------------------
+    if world == 1:
+        if only in (None, "prefill_c2"):
+            res, _b, _s = run_prefill(torch, low, ffi, dev, "prefill_c2", K, W, peaks)
+            workloads["prefill_c2"] = compact(res)
+            del _b, _s
             torch.cuda.empty_cache()
         if only in (None, "decode_c4"):
-            workloads["decode_c4"], _b = run_decode(torch, low, ffi, dev, "decode_c4", 64, 32, 8, 128, 16, 512, 8192,
-                                                    40000, max(K, 20), 5, peaks, seed=4)
-            del _b
+            workloads["decode_c4"] = compact(run_decode(torch, low, ffi, dev, "decode_c4", max(K, 20), 5, peaks))
             torch.cuda.empty_cache()
-
-    # ---- BASELINE.json configs[4]: the head-sharded shape, total work fixed, split over N GPUs ----
-    if not args.small and only in (None, "prefill_c5", "decode_c5", "c5"):
-        extra_steps = max(3, min(K, 10))
-        if only in (None, "prefill_c5", "c5"):
-            workloads["prefill_c5"] = run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, 1, 64, 8, 16384, 128,
-                                                          extra_steps, 3, peaks, seed=50, chunks=4)
+        if only in (None, "paged_prefill"):
+            # the step before decode: 1024-token chunks over paged contexts of 1024..8192 tokens, page 16
+            workloads["paged_prefill"] = compact(run_paged_prefill(torch, low, ffi, dev, "paged_prefill", 16, 1024, 32, 8, 128, 16,
+                                                                   1024, 8192, extra_steps, 3, peaks, seed=6))
             torch.cuda.empty_cache()
-        if only in (None, "decode_c5", "c5"):
-            workloads["decode_c5"] = run_sharded_decode(torch, low, ffi, dev, dist, world, rank, 256, 64, 8, 128, 16,
-                                                        1024, 32768, max(extra_steps, 10), 3, peaks, seed=51)
+        if only in (None, "varlen_prefill"):
+            # 32 prompts of 1024..8192 tokens packed, GQA 32/8
+            workloads["varlen_prefill"] = compact(run_varlen_prefill(torch, low, ffi, dev, "varlen_prefill", 32, 1024, 8192, 32, 8, 128,
+                                                                     extra_steps, 3, peaks, seed=7))
             torch.cuda.empty_cache()
+        if only in (None, "softmax_scores"):
+            # the scores of one head group of the GQA prefill on the math path, bf16
+            workloads["softmax_scores"] = compact(run_softmax(torch, low, ffi, dev, "softmax_scores", 131072, 4096, "bf16",
+                                                              extra_steps, 3, peaks, seed=8))
+            torch.cuda.empty_cache()
+        if only in (None, "prefill_c5"):
+            res, _c, _bufs = run_sharded_prefill(torch, low, ffi, dev, None, 1, 0, "prefill_c5", extra_steps, 3, peaks)
+            workloads["prefill_c5"] = compact(res)
+            del _bufs
+            torch.cuda.empty_cache()
+    else:
+        if only in (None, "prefill_c2"):
+            workloads["prefill_c2_weak"] = compact_weak(run_weak_prefill(torch, low, ffi, dev, dist, world, rank, "prefill_c2",
+                                                                          extra_steps, 3, peaks))
+            torch.cuda.empty_cache()
+    if only in (None, "decode_c5"):
+        workloads["decode_c5"] = compact(run_sharded_decode(torch, low, ffi, dev, dist, world, rank, "decode_c5",
+                                                            max(extra_steps, 10), 3, peaks))
+        torch.cuda.empty_cache()
 
     # ---- CPU baseline, rank 0, N == 1 only -----------------------------------------------------
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu and not args.small:
-        cpu, _ = cpu_baseline_prefill(4, 32, 32, 2048, 128)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline_prefill("prefill_c3")
 
     if rank == 0:
         line = {
             "metric": primary["metric"], "value": primary["value"], "unit": primary["unit"],
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": primary["ms_per_step"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": primary["scaling"], "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": primary["config"], "roofline": primary["roofline"],
-            "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "parity": primary["parity"],
             "gpu_launches": int(primary["launches_per_step"]) * K, "kernel_path": primary["kernel_path"],
-            "scaling_note": scaling_note, "workloads": workloads,
+            "workloads": workloads,
         }
+        if "peer_copy_gbs" in primary:
+            line["peer_copy_gbs"] = primary["peer_copy_gbs"]
+        if "per_gpu" in primary:
+            line["per_gpu"] = primary["per_gpu"]
+        if numa:
+            line["host_cpus"] = numa
         print(json.dumps(line))
+    ok = primary["parity"]["ok"] and all(w.get("parity_ok", True) for w in workloads.values())
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("parity check failed: the gathered output differs from a local recomputation")
+
+
+def compact_weak(res):
+    return {"value": round(res["value"], 1), "unit": res["unit"], "per_gpu": round(res["per_gpu"], 1), "ms": round(res["ms_per_step"], 4),
+            "scaling": "weak", "bound": "nvlink", "nvlink_out_gbs_per_gpu": round(res["roofline"]["achieved"], 1)}
 
 
 if __name__ == "__main__":

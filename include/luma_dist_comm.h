@@ -76,6 +76,12 @@ int luma_ipc_export(const void* ptr, void* handle_out, long long* offset_out);
 int luma_ipc_open(const void* handle, long long offset, void** ptr_out);
 int luma_ipc_close(void* ptr);
 
+/* One asynchronous copy between two device buffers that may live on different GPUs (a pointer from
+ * luma_ipc_open, or any device pointer of a process that enabled peer access): a point-to-point
+ * send as one cudaMemcpyAsync on `stream`. Used to measure the peer bandwidth that bounds the fused
+ * all-gather. No counterpart in the reference. */
+int luma_peer_copy(void* dst, const void* src, long long bytes, void* stream);
+
 const char* luma_comm_last_error(void);
 
 #ifdef __cplusplus

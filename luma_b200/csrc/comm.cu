@@ -362,6 +362,17 @@ int luma_ipc_open(const void* handle, long long offset, void** ptr_out) {
     return 0;
 }
 
+int luma_peer_copy(void* dst, const void* src, long long bytes, void* stream) {
+    g_comm_error[0] = '\0';
+    if (dst == nullptr || src == nullptr || bytes <= 0) return fail("luma_peer_copy: bad argument");
+    const cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail("luma_peer_copy: cudaMemcpyAsync: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
 int luma_ipc_close(void* ptr) {
     g_comm_error[0] = '\0';
     void* base = nullptr;

@@ -48,7 +48,7 @@ EXPORTED_SYMBOLS = (
     # include/luma_dist_comm.h
     + ["luma_comm_unique_id", "luma_comm_from_rank", "luma_comm_from_devices", "luma_comm_rank", "luma_comm_world_size",
        "luma_comm_device", "luma_comm_all_gather", "luma_comm_barrier", "luma_comm_destroy", "luma_ipc_export",
-       "luma_ipc_open", "luma_ipc_close", "luma_comm_last_error"]
+       "luma_ipc_open", "luma_ipc_close", "luma_peer_copy", "luma_comm_last_error"]
 )
 
 for _s in DTYPE_SUFFIX:
@@ -100,6 +100,7 @@ lib.luma_comm_destroy.argtypes = [c_void_p]
 lib.luma_ipc_export.argtypes = [c_void_p, c_void_p, c_void_p]
 lib.luma_ipc_open.argtypes = [c_void_p, ctypes.c_longlong, c_void_p]
 lib.luma_ipc_close.argtypes = [c_void_p]
+lib.luma_peer_copy.argtypes = [c_void_p, c_void_p, ctypes.c_longlong, c_void_p]
 lib.luma_comm_last_error.argtypes = []
 lib.luma_comm_last_error.restype = c_char_p
 lib.flash_attn_kvcache_append.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -112,7 +112,7 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens, block_table,
 
 
 class _HostPipe:
-    """Streams, events and device staging buffers of `flash_attn_func_host`, kept per device."""
+    """Streams and device staging buffers of `flash_attn_func_host`, kept per device."""
 
     def __init__(self, device):
         self.device = device
@@ -120,26 +120,37 @@ class _HostPipe:
         self.s_run = torch.cuda.Stream(device)
         self.s_out = torch.cuda.Stream(device)
         self.key = None
-        self.slots = []
+        self.kv = []      # two (k, v) device buffers: batch elements alternate
+        self.rows = []    # two (q chunk, o chunk) device buffers: row chunks alternate
 
-    def buffers(self, key, make):
+    def buffers(self, key, make_kv, make_rows):
         if self.key != key:
-            self.slots = [make() for _ in range(2)]
+            self.kv = [make_kv() for _ in range(2)]
+            self.rows = [make_rows() for _ in range(2)]
             self.key = key
-        return self.slots
+        return self.kv, self.rows
 
 
 _host_pipes = {}
 
 
+def _host_chunk_rows(sq: int) -> int:
+    """Query rows per pipeline step: a quarter of the sequence, in whole 128-row tiles, at least 1024."""
+    if sq < 4096:
+        return sq
+    return max(1024, ((sq + 3) // 4 + 127) // 128 * 128)
+
+
 def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = None, causal: bool = True,
-                         start_pos: int = 0, device=None):
+                         start_pos: int = 0, device=None, chunk_rows: Optional[int] = None):
     """Batched attention for HOST tensors (this library's addition; luma has no counterpart).
 
     q (B, Sq, Hq, d), k, v (B, Skv, Hkv, d) in (preferably pinned) host memory -> `out` (B, Sq, Hq, d)
-    in host memory (allocated pinned when None). The batch elements are independent, so they are
-    pipelined one at a time over three streams: while element i is in the kernel, element i+1 is
-    on its way to the device and the result of element i-1 on its way back, which keeps both
+    in host memory (allocated pinned when None). The work is cut into steps of one batch element and
+    `chunk_rows` query rows (a chunked prefill: the rows of a chunk see the keys up to their own
+    position, so a chunk needs only the K/V rows up to its end, which travel with it) and the steps are
+    pipelined over three streams: while one chunk is in the kernel, the next chunk's q rows and K/V rows
+    are on their way to the device and the previous chunk's result on its way back, which keeps both
     directions of the host link busy instead of using them in turn. The caller's current stream
     waits for the last copy; `out` is complete when that stream has caught up.
     """
@@ -157,6 +168,8 @@ def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = Non
         raise E.InvalidShape(f"flash_attn_func_host: incompatible shapes q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
     if k.dtype != q.dtype or v.dtype != q.dtype:
         raise E.Unsupported("flash_attn_func_host: q/k/v dtypes differ")
+    if start_pos < 0:
+        raise E.InvalidStartPos(f"start_pos={start_pos}")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(d)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -164,49 +177,68 @@ def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = Non
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
     elif out.is_cuda or tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
         raise E.InvalidShape("flash_attn_func_host: out must be a contiguous host tensor shaped and typed like q")
+    rows = int(chunk_rows) if chunk_rows else _host_chunk_rows(sq)
+    rows = max(1, min(rows, sq))
 
     pipe = _host_pipes.get(dev)
     if pipe is None:
         pipe = _host_pipes[dev] = _HostPipe(dev)
-    key = (sq, skv, hq, hkv, d, q.dtype)
+    key = (sq, skv, hq, hkv, d, q.dtype, rows)
 
-    def make():
-        return {"q": torch.empty((1, sq, hq, d), dtype=q.dtype, device=dev),
-                "k": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
-                "v": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
-                "o": torch.empty((1, sq, hq, d), dtype=q.dtype, device=dev),
-                "ran": None, "out": None}
+    def make_kv():
+        return {"k": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
+                "v": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev), "ran": None}
 
-    slots = pipe.buffers(key, make)
+    def make_rows():
+        return {"q": torch.empty((1, rows, hq, d), dtype=q.dtype, device=dev),
+                "o": torch.empty((1, rows, hq, d), dtype=q.dtype, device=dev), "ran": None, "out": None}
+
+    kv_slots, row_slots = pipe.buffers(key, make_kv, make_rows)
     cur = torch.cuda.current_stream(dev)
     start = torch.cuda.Event()
     start.record(cur)
     pipe.s_in.wait_event(start)
     last = None
+    step = 0
     for i in range(b):
-        sl = slots[i & 1]
-        # the slot's inputs are free once its previous kernel has run, its output once copied back
-        if sl["ran"] is not None:
-            pipe.s_in.wait_event(sl["ran"])
-        with torch.cuda.stream(pipe.s_in):
-            sl["q"].copy_(q[i:i + 1], non_blocking=True)
-            sl["k"].copy_(k[i:i + 1], non_blocking=True)
-            sl["v"].copy_(v[i:i + 1], non_blocking=True)
-            arrived = torch.cuda.Event()
-            arrived.record(pipe.s_in)
-        pipe.s_run.wait_event(arrived)
-        if sl["out"] is not None:
-            pipe.s_run.wait_event(sl["out"])
-        low.flash_attn(sl["q"], sl["k"], sl["v"], sl["o"], 1, sq, skv, hq, hkv, d, int(start_pos), scale, None,
-                       pipe.s_run, None)
-        sl["ran"] = torch.cuda.Event()
-        sl["ran"].record(pipe.s_run)
-        pipe.s_out.wait_event(sl["ran"])
-        with torch.cuda.stream(pipe.s_out):
-            out[i:i + 1].copy_(sl["o"], non_blocking=True)
-            sl["out"] = torch.cuda.Event()
-            sl["out"].record(pipe.s_out)
-        last = sl["out"]
+        kv = kv_slots[i & 1]
+        if kv["ran"] is not None:          # the last kernel that read this K/V buffer
+            pipe.s_in.wait_event(kv["ran"])
+        kv_have = 0                        # K/V rows of this batch element already on the device
+        for r0 in range(0, sq, rows):
+            r1 = min(sq, r0 + rows)
+            kv_need = min(skv, start_pos + r1)     # the chunk's rows see keys < start_pos + r1
+            sl = row_slots[step & 1]
+            step += 1
+            if sl["ran"] is not None:      # the slot's q is free once its previous kernel has run
+                pipe.s_in.wait_event(sl["ran"])
+            with torch.cuda.stream(pipe.s_in):
+                sl["q"][:, :r1 - r0].copy_(q[i:i + 1, r0:r1], non_blocking=True)
+                if kv_need > kv_have:
+                    kv["k"][:, kv_have:kv_need].copy_(k[i:i + 1, kv_have:kv_need], non_blocking=True)
+                    kv["v"][:, kv_have:kv_need].copy_(v[i:i + 1, kv_have:kv_need], non_blocking=True)
+                    kv_have = kv_need
+                arrived = torch.cuda.Event()
+                arrived.record(pipe.s_in)
+            pipe.s_run.wait_event(arrived)
+            if sl["out"] is not None:      # the slot's o is free once it has been copied back
+                pipe.s_run.wait_event(sl["out"])
+            if kv_need > 0:
+                low.flash_attn(sl["q"], kv["k"], kv["v"], sl["o"], 1, r1 - r0, kv_need, hq, hkv, d, int(start_pos) + r0,
+                               scale, None, pipe.s_run, None)
+            else:
+                with torch.cuda.stream(pipe.s_run):
+                    sl["o"].zero_()        # no key at all: the rows output zeros
+            ran = torch.cuda.Event()
+            ran.record(pipe.s_run)
+            sl["ran"] = ran
+            kv["ran"] = ran
+            pipe.s_out.wait_event(ran)
+            with torch.cuda.stream(pipe.s_out):
+                out[i:i + 1, r0:r1].copy_(sl["o"][:, :r1 - r0], non_blocking=True)
+                sl["out"] = torch.cuda.Event()
+                sl["out"].record(pipe.s_out)
+            last = sl["out"]
     if last is not None:
         cur.wait_event(last)
     return out

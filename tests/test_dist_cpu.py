@@ -64,7 +64,16 @@ def test_all_gather_heads_two_gloo_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(timeout=120)
+    finally:
+        for p in procs:   # a rank that stalled must not stay behind
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(10)
+    assert [p.exitcode for p in procs] == [0] * world
     assert dict(ret) == {0: True, 1: True}
