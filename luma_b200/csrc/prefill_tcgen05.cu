@@ -47,7 +47,12 @@ namespace {
 constexpr int kBlockM = 128;   // query rows per tile
 constexpr int kBlockN = 128;   // keys per K/V tile
 // head size D (64 or 128) is a template parameter of the kernel
-constexpr int kStages = 2;     // K ring and V ring depth
+constexpr int kStages = 2;     // K ring depth
+// V ring depth. Two, like K: a third stage fits the 227 KiB of shared memory and takes the MMA
+// issuer's ~350-clock wait for V out of every step (a bulk copy needs about 2 us to land while 148
+// CTAs stream their tiles out of L2, and a V stage is released later than a K stage), but measured
+// 5 % slower on every prefill workload (1165 against 1228 TFLOP/s at S = 8192, same box).
+constexpr int kStagesV = 2;
 constexpr int kThreads = 384;   // three warpgroups: softmax 0, softmax 1, and producer + issuer (+ two idle warps)
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
@@ -55,15 +60,20 @@ constexpr int kLoadWarpV = 10;   // V-ring producer (K ring and Q: kLoadWarp)
 constexpr int kHalfBytes = kBlockN * 64 * 2;   // 16 KiB: one 64-column half, 128 rows x 128 B
 template <int D> struct TileBytes { static constexpr int value = kBlockN * D * 2; };   // one half at D = 64, two at D = 128
 constexpr float kRescaleThreshold = 8.0f;            // log2 units
+// Which element pairs of an unmasked chunk take their exponential on the FMA pipe (a cubic) instead
+// of the special-function unit: one pair in eight. Measured on the S = 8192 GQA prefill, same box:
+// none 1231, one in eight 1237, one in four 1207, three in eight 1128, one in two 1058 TFLOP/s — the
+// cubic costs about as many issue slots as the special-function unit saves, so the share is small.
+__device__ __forceinline__ constexpr bool fma_pipe_exp(int i) { return (i & 7) == 7; }
 
 template <int D>
 struct SharedStorage {
     alignas(1024) unsigned char q[2][TileBytes<D>::value];
     alignas(1024) unsigned char k[kStages][TileBytes<D>::value];
-    alignas(1024) unsigned char v[kStages][TileBytes<D>::value];
+    alignas(1024) unsigned char v[kStagesV][TileBytes<D>::value];
     alignas(8) unsigned long long q_full[2];
     unsigned long long k_full[kStages], k_empty[kStages];
-    unsigned long long v_full[kStages], v_empty[kStages];
+    unsigned long long v_full[kStagesV], v_empty[kStagesV];
     unsigned long long s_full[2];   // MMA -> softmax: S_t ready (and every earlier MMA finished)
     unsigned long long p_lo[2];     // softmax -> MMA: keys 0-63 of P_t written, O_t rescaled
     unsigned long long p_hi[2];     // softmax -> MMA: keys 64-127 of P_t written
@@ -151,12 +161,15 @@ template <typename Storage>
 __device__ __forceinline__ bool mbar_wait(Storage& sm, unsigned long long* bar, unsigned parity, const PrefillArgs& a,
                                           int where) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    // the bound is counted in SM clocks (cheap to read, unlike the global nanosecond timer):
+    // wait_ns x 2 clocks, i.e. at least wait_ns of wall time at any SM clock up to 2 GHz
+    const long long t0 = clock64();
+    const long long limit = (long long)(a.wait_ns * 2ULL);
     for (unsigned spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (sm.abort_flag) return false;
-            if (global_timer_ns() - t0 > a.wait_ns) {
+            if (clock64() - t0 > limit) {
                 sm.abort_flag = 1;
                 *reinterpret_cast<volatile int*>(a.status) = where;
                 __threadfence_system();
@@ -513,6 +526,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sm.k_full[i], 1);
             mbar_init(&sm.k_empty[i], 1);
+        }
+        for (int i = 0; i < kStagesV; ++i) {
             mbar_init(&sm.v_full[i], 1);
             mbar_init(&sm.v_empty[i], 1);
         }
@@ -573,6 +588,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             unsigned long long* empty = is_v ? sm.v_empty : sm.k_empty;
             const CUtensorMap* map = is_v ? &v_map : &k_map;
             const void* kv_base = is_v ? a.v : a.k;
+            const int n_stages = is_v ? kStagesV : kStages;
             bool alive = true;
             if (!is_v) {   // what the set-up left out: Q tiles and first K tiles at the end of the packed buffers
                 if (q_edge(t0)) edge_tile_copy<D>(sm.q[0], a.q, a.q_heads, t0.head, (long long)sq.q_crow + t0.row0, tot_q, &sm.q_full[0], lane);
@@ -592,9 +608,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             bool tail_pending = false;   // the tail tile's copy was issued and v_tail not yet seen complete
             int issued = is_v ? 0 : n_pre;   // K tiles 0 .. n_pre-1 were issued during set-up
             for (int j = issued; j < n_max && alive; ++j) {
-                const int s = j % kStages;
-                if (j >= kStages) {
-                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &empty[s], ((unsigned)(j / kStages) & 1u) ^ 1u, a, is_v ? 2 : 1));
+                const int s = j % n_stages;
+                if (j >= n_stages) {
+                    alive = __all_sync(0xffffffffu, mbar_wait(sm, &empty[s], ((unsigned)(j / n_stages) & 1u) ^ 1u, a, is_v ? 2 : 1));
                     if (!alive) break;
                 }
                 const bool fix = tail_fix && j == tail_j;
@@ -632,16 +648,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     if (t1.valid) mbar_wait(sm, &sm.q_full[1], 0, a, 3);
                 }
                 const unsigned long long t_begin = global_timer_ns();
-                for (int s = 0; s < kStages; ++s) {
+                for (int s = 0; s < n_stages; ++s) {
                     if (issued <= s) continue;   // never filled
-                    const int last = issued - 1 - (issued - 1 - s) % kStages;   // last issued tile of this stage
+                    const int last = issued - 1 - (issued - 1 - s) % n_stages;   // last issued tile of this stage
                     if (!is_v && a.test_skip_k == last + 1) continue;          // test hook: never requested
                     if (tail_fix && last == tail_j) {
                         // that tile's copy completes on v_tail; the ring's barrier got (or, after an abort, never gets) a plain arrival
                         while (tail_pending && !mbar_try_wait(&sm.v_tail, 0u) && global_timer_ns() - t_begin < 100000000ULL) {}
                         continue;
                     }
-                    while (!mbar_try_wait(&full[s], (unsigned)(last / kStages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
+                    while (!mbar_try_wait(&full[s], (unsigned)(last / n_stages) & 1u) && global_timer_ns() - t_begin < 100000000ULL) {}
                 }
             }
         }
@@ -657,8 +673,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // rate — rebuilding the descriptors per product held it at ~90.
             const unsigned long long dq[2] = {make_desc(smem_u32(sm.q[0]), 16, 1024), make_desc(smem_u32(sm.q[1]), 16, 1024)};
             const unsigned long long dk[2] = {make_desc(smem_u32(sm.k[0]), 16, 1024), make_desc(smem_u32(sm.k[1]), 16, 1024)};
-            const unsigned long long dv[2] = {make_desc(smem_u32(sm.v[0]), kHalfBytes, 1024), make_desc(smem_u32(sm.v[1]), kHalfBytes, 1024)};
-            static_assert(kStages == 2, "descriptor tables above hold two stages");
+            const unsigned long long dv[3] = {make_desc(smem_u32(sm.v[0]), kHalfBytes, 1024), make_desc(smem_u32(sm.v[1]), kHalfBytes, 1024),
+                                              make_desc(smem_u32(sm.v[kStagesV - 1]), kHalfBytes, 1024)};
+            static_assert(kStages == 2 && (kStagesV == 3 || kStagesV == 2), "descriptor tables hold two K stages and up to three V stages");
             auto issue_s = [&](int t, int stage) {
                 // S_t = Q_t K^T : D / 16 K-steps over d; both operands K-major, 128 B swizzle
                 const unsigned long long qd = t ? dq[1] : dq[0];
@@ -674,7 +691,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             auto issue_pv = [&](int t, int stage, bool accumulate, int half) {
                 // O_t += P_t V : 8 K-steps of 16 keys; A = P from tensor memory (packed 16-bit, 8 columns
                 // per step), B = V MN-major: 64-column halves 16 KiB apart, 8-key groups 1 KiB apart
-                const unsigned long long vd = stage ? dv[1] : dv[0];
+                const unsigned long long vd = stage == 0 ? dv[0] : (stage == 1 ? dv[1] : dv[2]);
                 const unsigned d_tmem = tmem + 256 + t * 128;
                 const unsigned p_tmem = tmem + t * 128;
 #pragma unroll
@@ -699,12 +716,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tc_commit(&sm.k_empty[0]);
             }
             for (int j = 0; j < n_max && alive; ++j) {
-                const int s = j % kStages;
-                const unsigned ph = (unsigned)(j / kStages) & 1u;
-                const int s1 = (j + 1) % kStages;
+                const int s = j % kStagesV;                              // V stage of this step
+                const unsigned ph = (unsigned)(j / kStagesV) & 1u;
+                const int s1 = (j + 1) % kStages;                        // K stage of the next step
                 const unsigned ph1 = (unsigned)((j + 1) / kStages) & 1u;
                 alive = (mbar_wait(sm, &sm.v_full[s], ph, a, 13));
                 if (!alive) break;
+                FA_TRACE_EVENT(2, j, 4);
                 bool k_seen = j + 1 >= n_max;   // K(j+1) is first needed for S(j+1): looked at while P's second half is awaited
                 for (int t = 0; t < 2; ++t) {
                     if (j >= ts[t].n_kv) continue;
@@ -722,6 +740,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     }
                     alive = (mbar_wait(sm, &sm.p_hi[t], (unsigned)j & 1u, a, 16 + t));
                     if (!alive) break;
+                    FA_TRACE_EVENT(2, j, 5 + t);
                     tc_fence_after();
                     issue_pv(t, s, true, 1);
                     if (j + 1 < ts[t].n_kv) issue_s(t, s1);
@@ -861,7 +880,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         for (int i = 0; i < 16; ++i) {
                             float x0, x1, p0, p1;
                             unpack2(fma2(pack2(dv[k][2 * i], dv[k][2 * i + 1]), scale2, neg_m2), x0, x1);
-                            if ((i & 3) == 3) {
+                            if (fma_pipe_exp(i)) {
                                 ex2_fma2(x0, x1, p0, p1);
                             } else {
                                 p0 = ex2(x0);
@@ -953,7 +972,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                             const int ii = (i & 15) * 2;
                             float x0, x1, p0, p1;
                             unpack2(fma2(pack2(sv[cc][ii], sv[cc][ii + 1]), scale2, neg_m2), x0, x1);
-                            if (decltype(fma_pipe_share)::value && (i & 3) == 3) {
+                            if (decltype(fma_pipe_share)::value && fma_pipe_exp(i)) {
                                 ex2_fma2(x0, x1, p0, p1);
                             } else {
                                 p0 = ex2(x0);

@@ -9,7 +9,10 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libflash_attn.so"
+import os
+
+# the in-tree build; LUMA_B200_LIB names another build of the same library (e.g. one made with other -D flags)
+LIB_PATH = Path(os.environ.get("LUMA_B200_LIB") or (Path(__file__).resolve().parent / "lib" / "libflash_attn.so"))
 
 if not LIB_PATH.exists():
     raise ImportError(
@@ -138,6 +141,20 @@ def last_path() -> str:
 def device_status() -> int:
     """Synchronises, then reads and clears the device status word (0 = healthy)."""
     return int(lib.flash_attn_device_status())
+
+
+def _options_from_environment() -> None:
+    """LUMA_B200_OPTIONS="name=value,name=value" sets the library's integer knobs at import
+    (flash_attn_set_option), e.g. to run a test suite with another kernel variant."""
+    import os
+    for item in os.environ.get("LUMA_B200_OPTIONS", "").split(","):
+        name, sep, value = item.partition("=")
+        if sep and name.strip():
+            if lib.flash_attn_set_option(name.strip().encode(), int(value)) != 0:
+                raise KeyError(f"LUMA_B200_OPTIONS: unknown option {name.strip()!r}")
+
+
+_options_from_environment()
 
 
 def last_launches() -> int:

@@ -4,10 +4,12 @@ luma-nn/src/functional/attention.rs:13-117.
 `scaled_dot_product_attention(q, k, v, cfg)` picks the implementation the caller names in
 `AttentionConfig.imp` — there is deliberately no automatic choice (attention.rs:8-18):
 
-* `AttentionImpl.Math`  : the portable path built from core tensor ops (expand the KV heads, QK^T,
-  scale, causal mask by global position, softmax, PV — luma-tensor/src/ops/nn/attention.rs:11-45),
-  here on torch tensors of any device, differentiable. It is the cross-check of the fused path,
-  as in the reference's own tests (luma-nn/tests/attention.rs:190-235).
+* `AttentionImpl.Math`  : the device's provider. On host tensors the portable path built from core
+  tensor ops (expand the KV heads, QK^T, scale, causal mask by global position, softmax, PV —
+  luma-tensor/src/ops/nn/attention.rs:11-45), differentiable; it is the cross-check of the fused
+  path, as in the reference's own tests (luma-nn/tests/attention.rs:190-235). On CUDA tensors the
+  backend's override (`cuda_provide`), which takes the fused kernel for causal inference calls and the
+  same composed path otherwise.
 * `AttentionImpl.Flash` : the fused kernel behind `high.flash_attn_func`; CUDA tensors only, causal
   only, forward only — the same three guards, in the same order of concern, as attention.rs:76-100,
   and the library's errors come back as `FlashAttentionUnsupported` (attention.rs:110-117).
@@ -70,32 +72,15 @@ class AttentionConfig:
 
 
 def _math_path(q, k, v, scale, causal, start_pos):
-    """luma-tensor/src/ops/nn/attention.rs:11-45,95-127 on torch tensors: f32 math, output in q's dtype."""
-    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
-        raise NnError("scaled_dot_product_attention: q/k/v must be rank 4 (batch, seq, heads, head_size)")
-    b, sq, hq, d = q.shape
-    bk, skv, hkv, dk = k.shape
-    if tuple(v.shape) != tuple(k.shape) or bk != b or dk != d or hkv <= 0 or hq % hkv != 0:
-        raise NnError(f"scaled_dot_product_attention: incompatible shapes q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}")
-    s = float(scale) if scale is not None else 1.0 / math.sqrt(d)
-    group = hq // hkv
-    qf = q.float().permute(0, 2, 1, 3)                                   # (B, Hq, Sq, d)
-    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(group, dim=1)   # expand_heads (attention.rs:95-110)
-    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(group, dim=1)
-    scores = torch.matmul(qf, kf.transpose(-1, -2)) * s
-    if causal:
-        gpos = torch.arange(sq, device=q.device).unsqueeze(1) + int(start_pos)   # causal_mask (attention.rs:112-127)
-        keys = torch.arange(skv, device=q.device).unsqueeze(0)
-        scores = scores.masked_fill(keys > gpos, float("-inf"))
-    if scores.is_cuda and not (torch.is_grad_enabled() and scores.requires_grad):
-        # inference on a GPU: this library's row-softmax kernel (the reference's CUDA math path runs
-        # luma-cuda's softmax_f32 here); with autograd on, torch's differentiable softmax
-        from . import low
-        probs = low.softmax_last_dim(scores.contiguous(), out=None)
-    else:
-        probs = torch.softmax(scores, dim=-1)
-    out = torch.matmul(probs, vf).permute(0, 2, 1, 3)
-    return out.to(q.dtype).contiguous()
+    """AttentionImpl.Math: the provider's scaled_dot_product_attention of the tensors' device
+    (attention.rs:60-73 -> luma-tensor/src/device/nn_provide.rs:139-150). On host tensors that is the
+    composed default (luma-tensor/src/ops/nn/attention.rs:11-45,95-127); on CUDA tensors it is the
+    backend's override, which sends causal inference calls to the fused kernel and everything else —
+    gradients required, non-causal, other head sizes — to the same composed default."""
+    from . import cuda_provide
+    if q.is_cuda:
+        return cuda_provide.scaled_dot_product_attention(q, k, v, scale, causal, start_pos)
+    return cuda_provide.composed_default(q, k, v, scale, causal, start_pos)
 
 
 def scaled_dot_product_attention(q, k, v, cfg: AttentionConfig):

@@ -21,11 +21,21 @@ _DIR = Path(__file__).resolve().parent
 LIB_PATH = _DIR / "liboracle.so"
 
 
+def reference_root():
+    """Where the reference tree is mounted, if anywhere: the environment variable LUMA_REF_ROOT, else
+    a sibling `reference` directory of this repository's parent."""
+    env = os.environ.get("LUMA_REF_ROOT")
+    cand = Path(env) if env else _DIR.parent.parent / "reference"
+    return cand if (cand / "luma-flash-attn" / "kernels").is_dir() else None
+
+
 def build() -> Path:
-    """Compiles liboracle.so (and, where the reference tree is mounted, oracle/_ref)."""
+    """Compiles liboracle.so and, where the reference tree is mounted, the reference's own CUDA
+    kernels into oracle/_ref. A reference tree that is present but does not build is an error."""
     subprocess.run(["make", "-C", str(_DIR), "-s"], check=True)
-    if Path("/root/reference/luma-flash-attn/kernels").exists():
-        subprocess.run(["make", "-C", str(_DIR), "-s", "ref"], check=False)
+    ref = reference_root()
+    if ref is not None:
+        subprocess.run(["make", "-C", str(_DIR), "-s", "ref", f"REF_ROOT={ref}"], check=True)
     return LIB_PATH
 
 

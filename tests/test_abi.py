@@ -18,7 +18,7 @@ def _header_functions():
     names = set()
     for h in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
-        names |= set(re.findall(r"\b((?:flash_attn|luma_softmax|luma_comm|luma_ipc)_\w+)\s*\(", text))
+        names |= set(re.findall(r"\b((?:flash_attn|luma_softmax|luma_comm|luma_ipc|luma_peer)_\w+)\s*\(", text))
     return sorted(names)
 
 

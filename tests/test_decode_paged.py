@@ -34,7 +34,7 @@ def _run_decode(lens, hq, hkv, d, bs, dt, seed, scale=None, poison=True, chunk=0
 
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
 @pytest.mark.parametrize("hq,hkv,d,bs", [
-    (32, 8, 128, 16),   # BASELINE config 4 head layout
+    (32, 8, 128, 16),   # the head layout of the batch-64 decode benchmark (Hq=32, Hkv=8, d=128, page 16)
     (64, 8, 128, 16),   # config 5 head layout (group 8)
     (8, 8, 128, 16),    # MHA
     (16, 1, 64, 16),    # group 16, d=64

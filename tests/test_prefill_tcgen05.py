@@ -49,7 +49,7 @@ def test_prefill_matches_oracle(shape, dt):
 
 
 def test_prefill_matches_luma_cpu_math_path_config1_style():
-    # BASELINE config 1 layout (B=1, H=8, S=256, seed 0) at head size 128: compared with the f32
+    # the CPU-runnable case's layout (B=1, H=8, S=256, seed 0) at head size 128: compared with the f32
     # restatement of luma-cpu's math path, the oracle north_star names
     b, s, h, d = 1, 256, 8, 128
     q = H.round_to(H.normal((b, s, h, d), 0), "bf16")
