@@ -44,12 +44,14 @@ NOMINAL_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 NOMINAL_NVLINK_GBS = 900.0
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from
-# the ncu captures summarised under profiles/, as a ratio to the algorithmic bytes of the captured
-# case: the prefill captures are of prefill_c2 in full and of prefill_c3_small (B=1, 8 of 32 heads,
-# scaled to the full launch by the heads processed: traffic grows in proportion); the decode figure
-# is decode_c4_small (399.9 MB moved for 394.2 MB of algorithmic bytes, L2 hit rate 0.4 %).
-NCU_TRAFFIC_BYTES = {"prefill_c2": 512_585_728 + 51_621_632}
-NCU_DECODE_TRAFFIC_RATIO = (394_139_648 + 4_231_680) / 394_223_184
+# the ncu captures summarised under profiles/: the three prefill workloads were captured at full size
+# (five metrics, one or two passes); a head-sharded run divides the figure by the number of GPUs (every
+# GPU processes its share of the heads; q, k, v and o shard with them). The decode figure is the ratio
+# measured on decode_c4_small (397.9 MB moved for 394.2 MB of algorithmic bytes, L2 hit rate 0.1 %:
+# traffic grows in proportion to the cached tokens) applied to the run's own bytes.
+NCU_TRAFFIC_BYTES = {"prefill_c2": 509_276_160 + 47_899_648, "prefill_c3": 381_323_520 + 99_673_856,
+                     "prefill_c5": 666_307_840 + 230_259_968}
+NCU_DECODE_TRAFFIC_RATIO = (394_186_496 + 3_808_768) / 394_223_184
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # name -> (batch, q heads, kv heads, sequence, head size, seed, input scale, with LSE)
@@ -551,7 +553,9 @@ def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, wa
            "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
            "launches_per_step": launches[0], "config": prefill_config(name, world), "parity": parity,
            "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks, peer_gbs) if world > 1
-           else tensor_roofline(tf, peaks)}
+           else tensor_roofline(tf, peaks, NCU_TRAFFIC_BYTES.get(name))}
+    if world > 1 and NCU_TRAFFIC_BYTES.get(name):
+        res["roofline"]["traffic"] = NCU_TRAFFIC_BYTES[name] // world   # this GPU's share of the one-GPU capture
     if peer_gbs is not None:
         res["peer_copy_gbs"] = peer_gbs
     return res, clocks, (q, k, v)
