@@ -60,6 +60,7 @@ constexpr int kLoadWarpV = 10;   // V-ring producer (K ring and Q: kLoadWarp)
 constexpr int kHalfBytes = kBlockN * 64 * 2;   // 16 KiB: one 64-column half, 128 rows x 128 B
 template <int D> struct TileBytes { static constexpr int value = kBlockN * D * 2; };   // one half at D = 64, two at D = 128
 constexpr float kRescaleThreshold = 8.0f;            // log2 units
+
 // Which element pairs of an unmasked chunk take their exponential on the FMA pipe (a cubic) instead
 // of the special-function unit: one pair in eight. Measured on the S = 8192 GQA prefill, same box:
 // none 1231, one in eight 1237, one in four 1207, three in eight 1128, one in two 1058 TFLOP/s — the
