@@ -41,6 +41,18 @@ def unique_id() -> bytes:
     return buf.raw
 
 
+def gather_extents(shape, dim: int, elem_bytes: int):
+    """What luma_comm_all_gather takes for a dense tensor of `shape` gathered along `dim`:
+    (outer, chunk_bytes) = (product of the dims before `dim`, bytes of one rank's slab per outer index)."""
+    outer = 1
+    for s in shape[:dim]:
+        outer *= int(s)
+    chunk = int(elem_bytes)
+    for s in shape[dim:]:
+        chunk *= int(s)
+    return outer, chunk
+
+
 class Comm:
     """One rank's communicator. `all_gather(t, dim)` concatenates every rank's `t` along `dim`."""
 
@@ -79,12 +91,7 @@ class Comm:
             raise CommError("all_gather: the tensor must be a contiguous CUDA tensor")
         dim = dim % t.dim()
         shape = list(t.shape)
-        outer = 1
-        for s in shape[:dim]:
-            outer *= int(s)
-        chunk = t.element_size()
-        for s in shape[dim:]:
-            chunk *= int(s)
+        outer, chunk = gather_extents(shape, dim, t.element_size())
         shape[dim] *= self.world_size
         if out is None:
             out = torch.empty(shape, dtype=t.dtype, device=t.device)
