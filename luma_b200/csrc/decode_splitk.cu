@@ -1,4 +1,4 @@
-// Paged-KV single-token decode for f16/bf16 storage, head_size 64 or 128.
+// Paged-KV single-token decode for f16/bf16 storage, head_size 32, 64 or 128.
 //
 // Replaces flash_attn_decode_kernel (luma-flash-attn/kernels/flash_attn_with_kvcache.cu:22-116;
 // launch :123-145), which walks the context one token at a time with one warp per query head and
@@ -113,11 +113,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Shared memory of one CTA:
 //   ring : kWarps x kStages x {K tile, V tile}, each tile kTile rows of D elements, 16-byte chunks
-//          XOR-swizzled by (row & 7) so ldmatrix reads are bank-conflict free
+//          XOR-swizzled by the row (row & 7; row & 3 at head_size 32, whose rows hold only four chunks) against
+//          ldmatrix bank conflicts
 //   after the loop the same bytes hold the per-warp partials for the cross-warp merge.
 template <int D>
 struct Smem {
     static constexpr int kRowBytes = D * 2;
+    static constexpr int kSwz = (D / 8 - 1) < 7 ? (D / 8 - 1) : 7;   // XOR mask of the 16-byte chunk index: stays inside the row
     static constexpr int kTileBytes = kTile * kRowBytes;
     static constexpr int kStageBytes = 2 * kTileBytes;
     static constexpr int kWarpBytes = kStages * kStageBytes;
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
                 const long long off = __shfl_sync(0xffffffffu, my_off, row);
                 const bool valid = off >= 0;
                 const long long src = (valid ? off : 0) + cp_ch * 8;
-                const int dst = row * S::kRowBytes + ((cp_ch ^ (row & 7)) << 4);
+                const int dst = row * S::kRowBytes + ((cp_ch ^ (row & S::kSwz)) << 4);
                 cp_async_16(kst + dst, kg + src, valid);
                 cp_async_16(vst + dst, vg + src, valid);
             }
@@ -242,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
             for (int kk = 0; kk < kKSteps; ++kk) {
                 const int ch = 2 * kk + (mi & 1);
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, kst + tok * S::kRowBytes + ((ch ^ (tok & 7)) << 4));
+                ldmatrix_x4(b0, b1, b2, b3, kst + tok * S::kRowBytes + ((ch ^ (tok & S::kSwz)) << 4));
                 mma_16816<T>(sc[0], qa[kk], b0, b1);
                 mma_16816<T>(sc[1], qa[kk], b2, b3);
             }
@@ -305,7 +307,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
             for (int n = 0; n < kDBlocks; n += 2) {
                 const int ch = n + (mi >> 1);
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4_trans(b0, b1, b2, b3, vst + tok * S::kRowBytes + ((ch ^ (tok & 7)) << 4));
+                ldmatrix_x4_trans(b0, b1, b2, b3, vst + tok * S::kRowBytes + ((ch ^ (tok & S::kSwz)) << 4));
                 mma_16816<T>(acc[n], pa, b0, b1);
                 mma_16816<T>(acc[n + 1], pa, b2, b3);
             }
@@ -498,16 +500,19 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
 int launch_decode_splitk(const AttnParams& p, cudaStream_t stream) {
     if (p.mode != MODE_KVCACHE || p.q_seq_len != 1) return -1;
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
-    if (p.head_size != 64 && p.head_size != 128) return -1;
+    if (p.head_size != 32 && p.head_size != 64 && p.head_size != 128) return -1;
     if (p.q_heads > 65535) return -1;
     // 16-byte cp.async needs 16-byte aligned rows
     if ((reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) return -1;
     if (reinterpret_cast<uintptr_t>(p.q) & 3) return -1;
     if (p.dtype == DT_BF16) {
         return p.head_size == 128 ? launch_typed<__nv_bfloat16, 128>(p, stream)
-                                  : launch_typed<__nv_bfloat16, 64>(p, stream);
+               : p.head_size == 64 ? launch_typed<__nv_bfloat16, 64>(p, stream)
+                                   : launch_typed<__nv_bfloat16, 32>(p, stream);
     }
-    return p.head_size == 128 ? launch_typed<__half, 128>(p, stream) : launch_typed<__half, 64>(p, stream);
+    return p.head_size == 128 ? launch_typed<__half, 128>(p, stream)
+           : p.head_size == 64 ? launch_typed<__half, 64>(p, stream)
+                               : launch_typed<__half, 32>(p, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

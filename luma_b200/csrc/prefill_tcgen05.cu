@@ -1,6 +1,6 @@
 // Causal, GQA-capable flash-attention prefill forward for sm_100a: TMA-fed Q/K/V tiles,
 // tcgen05.mma with the S and O accumulators in tensor memory, online softmax in registers,
-// warp-specialised roles. Handles f16/bf16 storage with head_size 64 or 128 (template parameter D;
+// warp-specialised roles. Handles f16/bf16 storage with head_size 128, 64, or 32 on zero-padded 64-column tiles (template parameter D;
 // the layout comments below give the D = 128 figures) for the batched entry point (optional
 // key-padding mask: template parameter kMask), chunked prefill over a paged cache, and the packed varlen entry point (with
 // or without the packed buffers' row counts). Replaces flash_attn_kernel
@@ -111,6 +111,7 @@ struct PrefillArgs {
     long long* cta_log;  // optional per-CTA {start ns, end ns, SM id} records ("prefill_trace" = 3), up to kCtaLogEntries
 #endif
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
+    int d_real;     // head size of the tensors: D, or 32 when the D = 64 kernel runs a head size of 32 on zero-padded tiles
     int band;       // tile pairs of one (batch, KV head) that sit next to each other in blockIdx.x
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
     int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
@@ -451,8 +452,8 @@ __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const SeqExte
 // chunks XOR-swizzled by the row. The barrier's phase is completed by one plain arrival.
 template <int D>
 __device__ __forceinline__ void edge_tile_copy(unsigned char* dst, const void* base, int heads, int head, long long row_start,
-                                               long long total_rows, unsigned long long* bar, int lane) {
-    constexpr int kChunksPerRow = D / 8;   // 16-byte chunks per row
+                                               long long total_rows, unsigned long long* bar, int lane, int d_real) {
+    constexpr int kChunksPerRow = D / 8;   // 16-byte chunks per row of the tile (columns past d_real are zeros)
     const long long left = total_rows - row_start;
     const int nrows = left < 0 ? 0 : (left > kBlockN ? kBlockN : (int)left);
     const unsigned char* src = static_cast<const unsigned char*>(base);
@@ -460,7 +461,7 @@ __device__ __forceinline__ void edge_tile_copy(unsigned char* dst, const void* b
     for (int idx = lane; idx < kBlockN * kChunksPerRow; idx += 32) {
         const int r = idx / kChunksPerRow, cc = idx % kChunksPerRow;
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (r < nrows) w = *reinterpret_cast<const uint4*>(src + ((row_start + r) * heads + head) * (long long)(D * 2) + cc * 16);
+        if (r < nrows && cc * 8 < d_real) w = *reinterpret_cast<const uint4*>(src + ((row_start + r) * heads + head) * (long long)(d_real * 2) + cc * 16);
         *reinterpret_cast<uint4*>(dst + (cc >> 3) * kHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4)) = w;
     }
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> tensor-core reads
@@ -592,10 +593,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const int n_stages = is_v ? kStagesV : kStages;
             bool alive = true;
             if (!is_v) {   // what the set-up left out: Q tiles and first K tiles at the end of the packed buffers
-                if (q_edge(t0)) edge_tile_copy<D>(sm.q[0], a.q, a.q_heads, t0.head, (long long)sq.q_crow + t0.row0, tot_q, &sm.q_full[0], lane);
-                if (q_edge(t1)) edge_tile_copy<D>(sm.q[1], a.q, a.q_heads, t1.head, (long long)sq.q_crow + t1.row0, tot_q, &sm.q_full[1], lane);
+                if (q_edge(t0)) edge_tile_copy<D>(sm.q[0], a.q, a.q_heads, t0.head, (long long)sq.q_crow + t0.row0, tot_q, &sm.q_full[0], lane, a.d_real);
+                if (q_edge(t1)) edge_tile_copy<D>(sm.q[1], a.q, a.q_heads, t1.head, (long long)sq.q_crow + t1.row0, tot_q, &sm.q_full[1], lane, a.d_real);
                 for (int j = 0; j < n_pre; ++j)
-                    if (kv_edge(j)) edge_tile_copy<D>(sm.k[j], a.k, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &sm.k_full[j], lane);
+                    if (kv_edge(j)) edge_tile_copy<D>(sm.k[j], a.k, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, &sm.k_full[j], lane, a.d_real);
             }
             // The sequence's last V tile, when the sequence does not end on a tile boundary, holds rows
             // that are not this sequence's: the unwritten rest of its last page, or the next sequence
@@ -619,7 +620,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (!is_v && a.test_skip_k == j + 1) {
                     // test hook: this tile is never requested, the issuer's wait for it runs out
                 } else if (kv_edge(j)) {
-                    edge_tile_copy<D>(ring[s], kv_base, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, bar, lane);
+                    edge_tile_copy<D>(ring[s], kv_base, a.kv_heads, kvh, (long long)sq.kv_crow + (long long)j * kBlockN, tot_k, bar, lane, a.d_real);
                 } else if (lane == 0) {
                     load_kv_tile<D>(a, sq, b, kvh, ring[s], map, bar, j);
                 }
@@ -1096,9 +1097,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     for (int it = 0; it < 32 / kRowsPerStep; ++it) {
                         const int rr = warp_row0 + it * kRowsPerStep + sub;
                         const int grow = ti.row0 + rr;
-                        if (grow < sq.q_len) {
+                        if (grow < sq.q_len && ch * 8 < a.d_real) {
                             const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * kRowBytes + ((ch ^ (rr & (kChunks - 1))) << 4));
-                            const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * D + ch * 8;
+                            const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * a.d_real + ch * 8;
                             // every GPU of a group starts its walk at a different buffer (peer0 = its own
                             // index + 1), so that at no time all of them store to the same GPU
                             int pe = a.peer0;
@@ -1254,18 +1255,21 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     const bool packed = p.mode == MODE_VARLEN;
     const int q_batch = packed ? 1 : p.num_seqs, q_rows = packed ? p.total_q : p.q_seq_len;
     const int k_batch = packed ? 1 : p.num_seqs, k_rows = packed ? p.total_k : p.kv_seq_len;
-    bool ok = encode_map(&qm, p.q, p.dtype, D, q_batch, q_rows, p.q_heads);
+    // head size 32 runs on the D = 64 kernel: the maps carry the real inner extent (32), the 64-column
+    // boxes read zeros past it and bulk stores write nothing there
+    const int d_real = p.head_size;
+    bool ok = encode_map(&qm, p.q, p.dtype, d_real, q_batch, q_rows, p.q_heads);
     // The output as 32-row boxes (one per softmax warp). Bulk stores are used for a single, local output
     // only: a head-sharded call (n_out > 0) stores every copy with plain stores, and no tensor map is
     // ever made over another GPU's memory — the kernel's fourth map is then a second one over q, unused.
     if (p.n_out > 0) om = qm;
-    else ok = ok && encode_map(&om, p.o, p.dtype, D, q_batch, q_rows, p.q_heads, 32);
+    else ok = ok && encode_map(&om, p.o, p.dtype, d_real, q_batch, q_rows, p.q_heads, 32);
     if (p.paged) {
-        ok = ok && encode_paged_map(&km, p.k, p.dtype, D, p.block_size, p.kv_heads) &&
-             encode_paged_map(&vm, p.v, p.dtype, D, p.block_size, p.kv_heads);
+        ok = ok && encode_paged_map(&km, p.k, p.dtype, d_real, p.block_size, p.kv_heads) &&
+             encode_paged_map(&vm, p.v, p.dtype, d_real, p.block_size, p.kv_heads);
     } else {
-        ok = ok && encode_map(&km, p.k, p.dtype, D, k_batch, k_rows, p.kv_heads) &&
-             encode_map(&vm, p.v, p.dtype, D, k_batch, k_rows, p.kv_heads);
+        ok = ok && encode_map(&km, p.k, p.dtype, d_real, k_batch, k_rows, p.kv_heads) &&
+             encode_map(&vm, p.v, p.dtype, d_real, k_batch, k_rows, p.kv_heads);
     }
     if (!ok) return -1;  // let the SIMT kernel take it
     int* status = status_word();
@@ -1307,6 +1311,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
     a.q_heads = p.q_heads;
     a.kv_heads = p.kv_heads;
     a.start_pos = p.start_pos;
+    a.d_real = d_real;
     a.mode = p.mode;
     a.q = p.q;
     a.k = p.k;
@@ -1406,7 +1411,7 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     }
     if (p.paged && (p.block_size < 8 || p.block_size > 128 || (128 % p.block_size) != 0)) return -1;
     if (p.dtype != DT_F16 && p.dtype != DT_BF16) return -1;
-    if (p.head_size != 64 && p.head_size != 128) return -1;
+    if (p.head_size != 32 && p.head_size != 64 && p.head_size != 128) return -1;
     if (!(p.scale > 0.0f)) return -1;
     // (single-token calls of the kv-cache entry point never get here: the dispatcher tries the split-K
     // decode kernel first; single rows through the batched or packed entry points do)
@@ -1417,7 +1422,7 @@ int launch_prefill_tcgen05(const AttnParams& p, cudaStream_t stream) {
     const long long pairs = ((long long)(p.q_heads / p.kv_heads) * ((p.q_seq_len + kBlockM - 1) / kBlockM) + 1) / 2;
     if (pairs > 65535) return -1;
     const bool masked = p.mask != nullptr;
-    if (p.head_size == 64) {
+    if (p.head_size == 64 || p.head_size == 32) {
         if (p.dtype == DT_BF16) return masked ? launch_typed<__nv_bfloat16, 64, true>(p, stream) : launch_typed<__nv_bfloat16, 64, false>(p, stream);
         return masked ? launch_typed<__half, 64, true>(p, stream) : launch_typed<__half, 64, false>(p, stream);
     }
