@@ -467,6 +467,15 @@ def measure_peer_copy_gbs(torch, ffi, dist, dev, peer, rank, world, nbytes):
     return nbytes / float(t.item()) / 1e9
 
 
+def args_no_multicast():
+    """The fused all-gather stores to every peer with plain stores unless LUMA_B200_MULTICAST=1 asks for
+    the NVSwitch multicast form (one multimem.st per 16 bytes). An all-gather is bound by what must ENTER
+    each GPU, which multicast does not reduce (it adds the GPU's own shard to it): measured on 2 GPUs the
+    NVLink-bound weak-scaled workload ran at 1083 TFLOP/s with multicast against 1283 with plain stores,
+    the compute-bound strong-scaled one the same either way."""
+    return os.environ.get("LUMA_B200_MULTICAST", "") in ("", "0")
+
+
 def fused_roofline(flops_per_gpu, nvlink_out_bytes_per_gpu, sec_per_step, peaks, peer_gbs):
     """Roofline of the fused attention + all-gather kernel, per GPU: the target time is the slower of
     FLOPs / measured GEMM peak and bytes stored to peers over NVLink / the peer bandwidth measured in
@@ -497,7 +506,10 @@ def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, wa
     launches = [0]
     peer_gbs = None
     if world > 1:
-        peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
+        # plain peer stores by default; LUMA_B200_MULTICAST=1: symmetric allocation and, where the box offers
+        # an NVSwitch multicast address, stores through it
+        peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev, multicast=not args_no_multicast())
+        gather = "multimem.st through an NVSwitch multicast address" if peer.mc_ptr else "plain stores to every peer"
         peer_gbs = measure_peer_copy_gbs(torch, ffi, dist, dev, peer, rank, world, min(256 << 20, peer.out.numel() * 2))
         out = peer.out
 
@@ -552,12 +564,13 @@ def run_sharded_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, wa
     res = {"metric": "prefill attn TFLOP/s", "value": tf, "unit": "TFLOP/s", "per_gpu": tf / world,
            "ms_per_step": sec / steps * 1e3, "scaling": "strong", "n_gpus": world, "kernel_path": path,
            "launches_per_step": launches[0], "config": prefill_config(name, world), "parity": parity,
-           "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks, peer_gbs) if world > 1
+           "roofline": fused_roofline(flops / world, q.numel() * 2 * (world - 1), sec / steps, peaks, peer_gbs) if world > 1   # bytes that must enter every GPU
            else tensor_roofline(tf, peaks, NCU_TRAFFIC_BYTES.get(name))}
     if world > 1 and NCU_TRAFFIC_BYTES.get(name):
         res["roofline"]["traffic"] = NCU_TRAFFIC_BYTES[name] // world   # this GPU's share of the one-GPU capture
     if peer_gbs is not None:
         res["peer_copy_gbs"] = peer_gbs
+        res["gather"] = gather
     return res, clocks, (q, k, v)
 
 
@@ -627,7 +640,7 @@ def run_weak_prefill(torch, low, ffi, dev, dist, world, rank, name, steps, warmu
     from luma_b200 import dist as fdist
     b, hq, hkv, s, d, seed, scale_in, _lse = PREFILL[name]
     q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed + rank, scale_in)
-    peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq * world, d), torch.bfloat16, dev)
+    peer = fdist.PeerOutput(dist.group.WORLD, (b, s, hq * world, d), torch.bfloat16, dev, multicast=not args_no_multicast())
 
     def step():
         peer.fused_attention(q, k, v, hq * world, hq * rank)
@@ -895,6 +908,7 @@ def main():
         }
         if "peer_copy_gbs" in primary:
             line["peer_copy_gbs"] = primary["peer_copy_gbs"]
+            line["gather"] = primary["gather"]
         if "per_gpu" in primary:
             line["per_gpu"] = primary["per_gpu"]
         if numa:

@@ -222,6 +222,24 @@ int flash_attn_bf16_allgather_lse(const flash_attn_bf16_t* q, const flash_attn_b
                                   int kv_num_heads, int head_size, int start_pos, float scale, void* stream);
 
 /*
+ * The same fused all-gather through an NVSwitch multicast address: o_multicast is a device address that
+ * the caller obtained by binding the full (batch, q_seq_len, q_heads_total, head_size) output tensors of
+ * all GPUs of the group to one multicast object (cuMulticastCreate / cuMulticastBindMem, or a library
+ * that does it); the epilogue issues ONE multimem.st per 16 bytes and the switch writes it into every
+ * GPU's tensor, this GPU's own included, so that a GPU's outgoing volume is its shard once instead of
+ * once per peer. Everything else as flash_attn_<T>_allgather (barrier by the caller before reading;
+ * lse is local). No counterpart in the reference.
+ */
+int flash_attn_f16_allgather_multicast(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                       void* o_multicast, int q_heads_total, int q_head_offset, float* lse, int batch,
+                                       int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                                       int start_pos, float scale, void* stream);
+int flash_attn_bf16_allgather_multicast(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                        void* o_multicast, int q_heads_total, int q_head_offset, float* lse, int batch,
+                                        int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                                        int start_pos, float scale, void* stream);
+
+/*
  * Head-sharded single-token paged decode (q_seq_len == 1) with the output all-gather fused into the
  * split-K merge kernel: every merged row is stored straight into the (num_seqs, 1, q_heads_total,
  * head_size) output of every GPU of the group at head index q_head_offset (plain stores, as above).
@@ -318,6 +336,7 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *                             3 = log {start ns, end ns, SM id} of up to 2048 CTAs from byte 16384
  *       "prefill_trace_y"     blockIdx.y of the CTA whose timeline is recorded (0 = heaviest)
  *       "prefill_band"        tile pairs of one K/V stream launched next to each other (0 = automatic)
+ *       "prefill_order"       1 = heaviest-first launch order also for head-sharded calls (0 = their first wave mixes all weights)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  *       "prefill_wait_us"     bound of every wait inside the tcgen05 prefill kernel, microseconds
  *                             (0 = the default of 2 s)

@@ -26,6 +26,7 @@ std::atomic<int> g_decode_chunk{0};
 std::atomic<int> g_prefill_trace{0};
 std::atomic<int> g_prefill_trace_y{0};
 std::atomic<int> g_prefill_band{0};
+std::atomic<int> g_prefill_order{0};
 std::atomic<int> g_prefill_wait_us{0};
 std::atomic<int> g_prefill_test_skip_k{0};
 }  // namespace
@@ -49,6 +50,7 @@ int get_option_decode_chunk() { return g_decode_chunk.load(std::memory_order_rel
 int get_option_prefill_trace() { return g_prefill_trace.load(std::memory_order_relaxed); }
 int get_option_prefill_trace_y() { return g_prefill_trace_y.load(std::memory_order_relaxed); }
 int get_option_prefill_band() { return g_prefill_band.load(std::memory_order_relaxed); }
+int get_option_prefill_order() { return g_prefill_order.load(std::memory_order_relaxed); }
 int get_option_prefill_wait_us() { return g_prefill_wait_us.load(std::memory_order_relaxed); }
 int get_option_prefill_test_skip_k() { return g_prefill_test_skip_k.load(std::memory_order_relaxed); }
 
@@ -317,7 +319,7 @@ int varlen_impl(int dtype, const void* q, const void* k, const void* v, void* o,
 int allgather_impl(int dtype, const void* q, const void* k, const void* v, void* const* o_peers, int n_peers,
                    int q_heads_total, int q_head_offset, float* lse, int batch, int q_seq_len, int kv_seq_len,
                    int q_num_heads, int kv_num_heads, int head_size, int start_pos, float scale, void* stream,
-                   float* const* lse_peers = nullptr) {
+                   float* const* lse_peers = nullptr, int multicast = 0) {
     g_last_error[0] = '\0';
     cudaGetLastError();
     if (q == nullptr || k == nullptr || v == nullptr || o_peers == nullptr) {
@@ -377,6 +379,7 @@ int allgather_impl(int dtype, const void* q, const void* k, const void* v, void*
     p.scale = scale;
     for (int i = 0; i < n_peers; ++i) p.o_peers[i] = o_peers[i];
     p.n_out = n_peers;
+    p.multicast = multicast;
     p.o_heads = q_heads_total;
     p.o_head0 = q_head_offset;
     if (lse_peers != nullptr) {
@@ -513,6 +516,10 @@ int flash_attn_set_option(const char* name, int value) {
         fa::g_prefill_trace = value;
         return 0;
     }
+    if (std::strcmp(name, "prefill_order") == 0) {
+        fa::g_prefill_order = value;
+        return 0;
+    }
     if (std::strcmp(name, "prefill_band") == 0) {
         fa::g_prefill_band = value;
         return 0;
@@ -632,6 +639,25 @@ int flash_attn_bf16_allgather_lse(const flash_attn_bf16_t* q, const flash_attn_b
                                   int kv_num_heads, int head_size, int start_pos, float scale, void* stream) {
     return fa::allgather_impl(fa::DT_BF16, q, k, v, o_peers, n_peers, q_heads_total, q_head_offset, nullptr, batch, q_seq_len,
                               kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream, lse_peers);
+}
+
+int flash_attn_f16_allgather_multicast(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                                       void* o_multicast, int q_heads_total, int q_head_offset, float* lse, int batch,
+                                       int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                                       int start_pos, float scale, void* stream) {
+    void* one[1] = {o_multicast};
+    return fa::allgather_impl(fa::DT_F16, q, k, v, o_multicast != nullptr ? one : nullptr, 1, q_heads_total, q_head_offset, lse,
+                              batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream,
+                              nullptr, 1);
+}
+int flash_attn_bf16_allgather_multicast(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                                        void* o_multicast, int q_heads_total, int q_head_offset, float* lse, int batch,
+                                        int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads, int head_size,
+                                        int start_pos, float scale, void* stream) {
+    void* one[1] = {o_multicast};
+    return fa::allgather_impl(fa::DT_BF16, q, k, v, o_multicast != nullptr ? one : nullptr, 1, q_heads_total, q_head_offset, lse,
+                              batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale, stream,
+                              nullptr, 1);
 }
 
 int flash_attn_with_kvcache_f16_allgather(const flash_attn_f16_t* q, const flash_attn_f16_t* k_cache,

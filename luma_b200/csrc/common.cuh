@@ -54,6 +54,7 @@ struct AttnParams {
     // (batch, q_seq_len, o_heads, head_size) that each receive this call's heads at o_head0
     void* o_peers[8];
     int n_out;
+    int multicast;              // o_peers[0] is an NVSwitch multicast address of the group's output tensors (n_out == 1)
     int o_heads;
     int o_head0;
     // the same for the log-sum-exp: n_lse > 0 buffers of (batch, o_heads, q_seq_len) f32
@@ -128,6 +129,7 @@ int get_option_decode_chunk();
 int get_option_prefill_trace();
 int get_option_prefill_trace_y();
 int get_option_prefill_band();
+int get_option_prefill_order();         // 1 = heaviest-first launch order even for head-sharded calls (0 = the default)
 int get_option_prefill_wait_us();       // bound of the tcgen05 kernel's waits in microseconds (0 = the default, 2 s)
 int get_option_prefill_test_skip_k();   // test hook: 1 + index of a K tile the producer never requests (0 = off)
 

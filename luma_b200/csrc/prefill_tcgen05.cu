@@ -98,6 +98,7 @@ struct PrefillArgs {
     void* o[kMaxPeers];
     int n_out, o_heads, o_head0;
     int peer0;          // n_out > 1: the buffer this CTA's rows go to first; each CTA walks the buffers from there
+    int multicast;      // o[0] is an NVSwitch multicast address of the group's output tensors: one multimem.st reaches all of them
     float* lse;         // (batch, q_heads, q_seq_len) of this call, or null
     float* lse_peers[kMaxPeers];   // n_lse > 0: (batch, o_heads, q_seq_len) on every GPU of the group, written at head o_head0
     int n_lse;
@@ -113,6 +114,10 @@ struct PrefillArgs {
     int batch, q_seq_len, kv_seq_len, q_heads, kv_heads, start_pos;
     int d_real;     // head size of the tensors: D, or 32 when the D = 64 kernel runs a head size of 32 on zero-padded tiles
     int band;       // tile pairs of one (batch, KV head) that sit next to each other in blockIdx.x
+    // Launch order of the bands (blockIdx.y), heaviest = 0. spread_w == 0: heaviest first. Otherwise the
+    // first spread_w rows of the grid are every spread_m-th band (a first wave that mixes all weights,
+    // so that CTAs end at spread-out times from the start), the other bands follow heaviest first.
+    int spread_w, spread_m;
     // which entry point the problem came from (fa::Mode) and its per-sequence descriptors
     int mode;                   // MODE_BATCH: uniform q_seq_len / kv_seq_len / start_pos
     const void* q;              // MODE_VARLEN: the packed q / k / v buffers themselves, for the tiles at their very end
@@ -194,6 +199,13 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(map),
                  "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+// 16 bytes to an NVSwitch multicast address: the switch replicates the store into the same offset of
+// every GPU's memory bound to the multicast object (the bits are stored as they are).
+__device__ __forceinline__ void multimem_st16(void* mc_addr, const uint4& w) {
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(mc_addr), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w)
                  : "memory");
 }
 
@@ -495,7 +507,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int num_mb = (sq.q_len + kBlockM - 1) / kBlockM;
     const int kvh = stream_id % a.kv_heads;
     const int b = stream_id / a.kv_heads;
-    const int pair = (gridDim.y - 1 - blockIdx.y) * a.band + (a.band - 1 - (int)(blockIdx.x % a.band));
+    int rank_y = (int)blockIdx.y;   // this row's rank by weight, 0 = heaviest
+    if (a.spread_w > 0) {
+        const int by = (int)blockIdx.y, w = a.spread_w, m = a.spread_m;
+        if (by < w) rank_y = by * m;
+        else if (by - w < w * (m - 1)) rank_y = ((by - w) / (m - 1)) * m + 1 + (by - w) % (m - 1);
+        // (rows past w * m keep their index: by - w + w * (m - 1) + ... = by)
+    }
+    const int pair = ((int)gridDim.y - 1 - rank_y) * a.band + (a.band - 1 - (int)(blockIdx.x % a.band));
 
     const TileInfo t0 = tile_info(sq, pair, 0, kvh, group, num_mb);
     const TileInfo t1 = tile_info(sq, pair, 1, kvh, group, num_mb);
@@ -1018,7 +1037,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #else
             constexpr bool staged_only = false;
 #endif
-            const bool bulk_ok = a.n_out == 1 && !staged_only && (a.mode != MODE_VARLEN || ti.row0 + kBlockM <= sq.q_len);
+            const bool bulk_ok = a.n_out == 1 && !a.multicast && !staged_only && (a.mode != MODE_VARLEN || ti.row0 + kBlockM <= sq.q_len);
             if (bulk_ok) {
                 // Single output: the rows go out as bulk tensor stores. Each warp lays its 32 rows down in
                 // the Q tile's shared memory (every MMA that read Q_t has finished) in the 128-byte-swizzled
@@ -1102,10 +1121,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                             const long long o_off = ((sq.o_row0 + grow) * a.o_heads + a.o_head0 + ti.head) * a.d_real + ch * 8;
                             // every GPU of a group starts its walk at a different buffer (peer0 = its own
                             // index + 1), so that at no time all of them store to the same GPU
-                            int pe = a.peer0;
-                            for (int n = 0; n < a.n_out; ++n) {
-                                *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
-                                pe = pe + 1 == a.n_out ? 0 : pe + 1;
+                            if (a.multicast) {
+                                // one store into the multicast address: the switch writes it into every GPU's tensor
+                                multimem_st16(static_cast<T*>(a.o[0]) + o_off, w);
+                            } else {
+                                int pe = a.peer0;
+                                for (int n = 0; n < a.n_out; ++n) {
+                                    *reinterpret_cast<uint4*>(static_cast<T*>(a.o[pe]) + o_off) = w;
+                                    pe = pe + 1 == a.n_out ? 0 : pe + 1;
+                                }
                             }
                         }
                     }
@@ -1286,6 +1310,7 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         a.o_head0 = p.o_head0;
         // with equal shards this GPU's index in the group is o_head0 / q_heads: start one past it
         a.peer0 = (p.o_head0 / p.q_heads + 1) % p.n_out;
+        a.multicast = p.multicast;
     } else {
         a.o[0] = p.o;
         a.n_out = 1;
@@ -1348,6 +1373,22 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         if (get_option_prefill_band() > 0) band = std::min(get_option_prefill_band(), pairs);
     }
     a.band = band;
+    // Head-sharded call (every CTA ends with stores to the other GPUs): heaviest-first makes the SMs end
+    // their CTAs in waves, each wave a burst on the links that stalls every SM in it. A first wave that
+    // mixes all weights staggers the SMs for the rest of the launch; the rest stays heaviest first, which
+    // keeps the tail balanced.
+    {
+        const int rows = (pairs + band - 1) / band;
+        const int per_row = p.kv_heads * p.num_seqs * band;
+        int sms = 148;
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int w = (sms + per_row - 1) / per_row;
+        const int m = w > 0 ? rows / w : 0;
+        const bool spread = p.n_out > 1 && get_option_prefill_order() != 1 && m >= 2;
+        a.spread_w = spread ? w : 0;
+        a.spread_m = spread ? m : 0;
+    }
     if ((long long)p.kv_heads * p.num_seqs * band > 0x7fffffffLL) return -1;
     dim3 grid(p.kv_heads * p.num_seqs * band, (pairs + band - 1) / band);
     prefill_tcgen05_kernel<T, D, kMask><<<grid, kThreads, smem, stream>>>(qm, km, vm, om, a);

@@ -67,22 +67,53 @@ class PeerOutput:
     nothing here uses TMA or multicast). With `with_lse` a (B, Hq_total, S) f32 log-sum-exp tensor
     is shared the same way.
 
+    With `multicast=True` the output is allocated as symmetric memory (torch.distributed._symmetric_memory:
+    the same allocation on every rank, bound to one NVSwitch multicast object where the hardware and the
+    driver offer it) and `fused_attention` stores through the multicast address: one `multimem.st` per 16
+    bytes reaches every rank's copy, so a GPU sends its shard once instead of once per peer. Where
+    multicast is not on offer (`self.mc_ptr == 0`, agreed across the group) the peer-pointer path is used.
+
     `fused_attention` runs the head-sharded prefill with the gather fused into its epilogue,
     `fused_decode` the head-sharded single-token decode with the gather fused into its merge kernel;
     `sync()` then synchronises the group, after which `self.out` (and `self.lse`) hold every rank's heads.
     """
 
-    def __init__(self, group, shape, dtype, device, with_lse=False):
+    def __init__(self, group, shape, dtype, device, with_lse=False, multicast=False):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.out = torch.empty(shape, dtype=dtype, device=device)
         self.lse = torch.empty((shape[0], shape[2], shape[1]), dtype=torch.float32, device=device) if with_lse else None
         self._opened = []        # mapped peer pointers, closed by close()
-        self.ptrs = self._exchange(self.out)
+        self._symm = None
+        self.mc_ptr = 0
+        self.out = None
+        if multicast:
+            self._try_symmetric(shape, dtype, device)
+        if self.out is None:
+            self.out = torch.empty(shape, dtype=dtype, device=device)
+            self.ptrs = self._exchange(self.out)
         self.lse_ptrs = self._exchange(self.lse) if with_lse else None
         self._flag = torch.zeros(1, device=device)
         dist.barrier(group=group)
+
+    def _try_symmetric(self, shape, dtype, device):
+        """Symmetric allocation + rendezvous; leaves self.out None when this build or box cannot do it."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            out = symm.empty(tuple(shape), dtype=dtype, device=device)
+            hdl = symm.rendezvous(out, self.group)
+            off = int(getattr(hdl, "offset", 0))
+            ptrs = [int(p) + off for p in hdl.buffer_ptrs]
+            ok = ptrs[self.rank] == out.data_ptr()
+            mc = int(hdl.multicast_ptr) if ok else 0
+        except Exception:   # noqa: BLE001 - any failure means: no symmetric memory here
+            out, hdl, ptrs, mc, off, ok = None, None, None, 0, 0, False
+        # every rank must take the same path
+        flag = torch.tensor([1 if ok else 0, 1 if mc else 0], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag[0]) == 1:
+            self.out, self._symm, self.ptrs = out, hdl, ptrs
+            self.mc_ptr = (mc + off) if int(flag[1]) == 1 else 0
 
     def _exchange(self, t):
         """Every rank's device pointer to its own copy of `t`, as seen from THIS process."""
@@ -128,6 +159,10 @@ class PeerOutput:
         if gather_lse:
             assert self.lse_ptrs is not None and row0 == 0 and sq == s_total
             lse_ptrs = self.lse_ptrs
+        if self.mc_ptr and lse_ptrs is None:
+            low.flash_attn_allgather_multicast(q, k, v, self.mc_ptr + off, q_heads_total, q_head_offset, b, sq, skv, hq_l,
+                                               hkv_l, d, int(start_pos), scale, None, lse)
+            return
         low.flash_attn_allgather(q, k, v, ptrs, q_heads_total, q_head_offset, b, sq, skv, hq_l, hkv_l, d,
                                  int(start_pos), scale, None, lse, lse_ptrs)
 
@@ -156,6 +191,8 @@ class PeerOutput:
         for p in self._opened:
             ffi.lib.luma_ipc_close(p)
         self._opened = []
+        self._symm = None
+        self.mc_ptr = 0
         self.ptrs = [self.out.data_ptr()]
         self.lse_ptrs = None
         torch.cuda.synchronize()

@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     + [f"flash_attn_{s}_lse" for s in DTYPE_SUFFIX]
     + ["flash_attn_decode_bf16_noalloc", "flash_attn_f16_allgather", "flash_attn_bf16_allgather",
        "flash_attn_f16_allgather_lse", "flash_attn_bf16_allgather_lse",
+       "flash_attn_f16_allgather_multicast", "flash_attn_bf16_allgather_multicast",
        "flash_attn_with_kvcache_f16_allgather", "flash_attn_with_kvcache_bf16_allgather",
        "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total",
        "flash_attn_release_workspaces"]
@@ -85,6 +86,10 @@ for _s in ("f16", "bf16"):
                                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                               c_float, c_void_p]
     getattr(lib, f"flash_attn_{_s}_allgather_lse").restype = c_int
+    getattr(lib, f"flash_attn_{_s}_allgather_multicast").argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                                    c_void_p]
+    getattr(lib, f"flash_attn_{_s}_allgather_multicast").restype = c_int
     getattr(lib, f"flash_attn_with_kvcache_{_s}_allgather").argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                                        c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                                        c_int, c_int, c_float, c_void_p]

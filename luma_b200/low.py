@@ -180,6 +180,22 @@ def flash_attn_allgather(q, k, v, o_peer_ptrs, q_heads_total, q_head_offset, bat
     E.from_status(code, ffi.last_error())
 
 
+def flash_attn_allgather_multicast(q, k, v, o_multicast_ptr, q_heads_total, q_head_offset, batch, q_seq_len, kv_seq_len,
+                                   q_num_heads, kv_num_heads, head_size, start_pos, scale, stream=None, lse=None) -> None:
+    """The fused all-gather through an NVSwitch multicast address of the group's output tensors: one
+    multimem.st per 16 bytes reaches every GPU's copy. Additive."""
+    sfx = _suffix(q)
+    if sfx == "f32":
+        raise E.Unsupported("flash_attn_allgather_multicast: f16/bf16 only")
+    _check_len("q", q.numel(), batch * q_seq_len * q_num_heads * head_size)
+    _check_len("k", k.numel(), batch * kv_seq_len * kv_num_heads * head_size)
+    _check_len("v", v.numel(), batch * kv_seq_len * kv_num_heads * head_size)
+    code = getattr(ffi.lib, f"flash_attn_{sfx}_allgather_multicast")(
+        _ptr(q), _ptr(k), _ptr(v), int(o_multicast_ptr), q_heads_total, q_head_offset, _ptr(lse), batch, q_seq_len, kv_seq_len,
+        q_num_heads, kv_num_heads, head_size, start_pos, scale, _stream_ptr(stream, q))
+    E.from_status(code, ffi.last_error())
+
+
 def flash_attn_with_kvcache_allgather(q, k_cache, v_cache, o_peer_ptrs, q_heads_total, q_head_offset, block_tables,
                                       context_lens, num_seqs, q_heads, kv_heads, head_size, block_size, max_blocks,
                                       scale, stream=None) -> None:

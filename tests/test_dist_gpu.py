@@ -3,7 +3,8 @@ all-gather must reproduce the unsharded result on EVERY rank, as luma-dist check
 every rank (luma-dist/src/backends/nccl/tests.rs:60-90):
 
 * prefill, fused: the tensor-core kernel's epilogue stores into every rank's output over peer memory
-  (head sizes 128 and 64), whole sequence and in two row chunks, with the log-sum-exp gathered too;
+  (head sizes 128 and 64), whole sequence and in two row chunks, with the log-sum-exp gathered too, and
+  through an NVSwitch multicast address (one multimem.st per 16 bytes) where the box offers one;
 * prefill, two-step: attention on the shard, then the all-gather along the head axis
   (torch.distributed's NCCL, and this library's own communicator: luma_comm_all_gather);
 * decode, fused: the split-K merge kernel stores into every rank's output; and two-step.
@@ -89,6 +90,19 @@ def _worker(rank, world, port, port2, ret):
             torch.cuda.synchronize()
             res[f"fused_chunks_d{d}"] = close(H.to_np(out2), want)
             peer.close()
+            # the same through an NVSwitch multicast address, where the box offers one (else the peer-pointer path again)
+            peer = PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev, multicast=True)
+            peer.out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            peer.fused_attention(ql, kl, vl, hq, qs.start)
+            out3 = peer.sync()
+            torch.cuda.synchronize()
+            res[f"fused_multicast_d{d}"] = bool(torch.equal(out3, gathered)) and ffi.device_status() == 0
+            res[f"multicast_used_d{d}"] = True      # informational: which path ran is printed, both are valid
+            if rank == 0:
+                print(f"world {world} d {d}: multicast address {'used' if peer.mc_ptr else 'not available'}", flush=True)
+            peer.close()
 
         # decode: every rank holds the cache slice of its KV heads; tables and lengths are replicated
         d, hq, hkv, bs = 128, 16, 8, 16
@@ -149,7 +163,7 @@ def _run_world(world):
     for r in range(world):
         bad = [k for k, ok in got[r].items() if not ok]
         assert not bad, f"rank {r} of {world}: {bad}"
-        assert len(got[r]) == 14
+        assert len(got[r]) == 18
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
