@@ -8,8 +8,9 @@ zero-fills the receive buffer, gathers, permutes back and materialises again
 ncclAllGather into a persistent (G, B*S, H_local*d) staging buffer and one strided copy into the
 final (B, S, G*H_local, d) tensor — no memset, no input-side copy.
 
-Partitioning (rank g of G): KV heads [g*Hkv/G, (g+1)*Hkv/G) and the Hq/Hkv query heads of each.
-G must divide Hkv. Block tables and context lengths are replicated.
+Partitioning (rank g of G): KV heads [g*Hkv/G, (g+1)*Hkv/G) and the Hq/Hkv query heads of each
+when G divides Hkv; with G a multiple of Hkv every KV head is replicated on G/Hkv ranks and its query
+heads are split among them. Block tables and context lengths are replicated.
 """
 from __future__ import annotations
 
@@ -20,16 +21,25 @@ import torch.distributed as dist
 
 
 def shard_heads(n_q_heads: int, n_kv_heads: int, world: int, rank: int) -> Tuple[slice, slice]:
-    """Query-head and KV-head slices owned by `rank`; whole KV groups stay together."""
-    if n_kv_heads % world != 0:
-        raise ValueError(f"world size {world} must divide kv heads {n_kv_heads}")
+    """Query-head and KV-head slices owned by `rank`. While the world divides the KV heads, whole KV
+    groups stay together. With more ranks than KV heads (the world a multiple of them) every KV head is
+    replicated on world / n_kv_heads ranks and its group of query heads is split evenly among them; the
+    query slices still tile the head axis in rank order, so the all-gather along it is unchanged."""
     if n_q_heads % n_kv_heads != 0:
         raise ValueError("q heads must be a multiple of kv heads")
-    kv_per = n_kv_heads // world
     group = n_q_heads // n_kv_heads
-    kv = slice(rank * kv_per, (rank + 1) * kv_per)
-    q = slice(kv.start * group, kv.stop * group)
-    return q, kv
+    if n_kv_heads % world == 0:
+        kv_per = n_kv_heads // world
+        kv = slice(rank * kv_per, (rank + 1) * kv_per)
+        return slice(kv.start * group, kv.stop * group), kv
+    if world % n_kv_heads == 0 and group % (world // n_kv_heads) == 0:
+        replicas = world // n_kv_heads            # ranks that share one KV head
+        per = group // replicas                   # query heads of that group per rank
+        head = rank // replicas
+        q0 = head * group + (rank % replicas) * per
+        return slice(q0, q0 + per), slice(head, head + 1)
+    raise ValueError(f"world size {world} must divide kv heads {n_kv_heads}, or be a multiple of them that divides "
+                     f"the {group} query heads of a group")
 
 
 class HeadAllGather:

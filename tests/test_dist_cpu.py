@@ -23,8 +23,20 @@ def test_shard_heads_keeps_kv_groups_together():
             seen_q += list(range(q.start, q.stop))
             seen_kv += list(range(kv.start, kv.stop))
         assert seen_q == list(range(64)) and seen_kv == list(range(8))
+    # more ranks than KV heads: every KV head is replicated and its query heads are split
+    for hq, hkv, world in ((32, 2, 8), (64, 8, 16), (8, 1, 4)):
+        seen_q = []
+        for rank in range(world):
+            q, kv = shard_heads(hq, hkv, world, rank)
+            assert kv.stop - kv.start == 1 and kv.start == rank // (world // hkv)
+            assert q.stop - q.start == hq // world
+            assert q.start // (hq // hkv) == kv.start and (q.stop - 1) // (hq // hkv) == kv.start   # inside that head's group
+            seen_q += list(range(q.start, q.stop))
+        assert seen_q == list(range(hq))
     with pytest.raises(ValueError):
         shard_heads(64, 8, 3, 0)
+    with pytest.raises(ValueError):
+        shard_heads(12, 4, 8, 0)      # 8 ranks over 4 KV heads would need the 3 heads of a group split in two
     with pytest.raises(ValueError):
         shard_heads(10, 4, 2, 0)
 

@@ -104,6 +104,24 @@ def _worker(rank, world, port, port2, ret):
                 print(f"world {world} d {d}: multicast address {'used' if peer.mc_ptr else 'not available'}", flush=True)
             peer.close()
 
+        # more ranks than KV heads: the one KV head is replicated on every rank, its 8 query heads are split
+        b, s, hq, hkv, d = 1, 384, 8, 1, 128
+        q = H.round_to(H.normal((b, s, hq, d), 41), "bf16")
+        k = H.round_to(H.normal((b, s, hkv, d), 42), "bf16")
+        v = H.round_to(H.normal((b, s, hkv, d), 43), "bf16")
+        want = ob.attn_f64_batch(q, k, v)
+        qs, kvs = shard_heads(hq, hkv, world, rank)
+        peer = PeerOutput(dist.group.WORLD, (b, s, hq, d), torch.bfloat16, dev)
+        peer.out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        peer.fused_attention(H.to_dev(q[:, :, qs], "bf16", dev).contiguous(), H.to_dev(k[:, :, kvs], "bf16", dev).contiguous(),
+                             H.to_dev(v[:, :, kvs], "bf16", dev).contiguous(), hq, qs.start)
+        out = peer.sync()
+        torch.cuda.synchronize()
+        res["replicated_kv_head"] = close(H.to_np(out), want)
+        peer.close()
+
         # decode: every rank holds the cache slice of its KV heads; tables and lengths are replicated
         d, hq, hkv, bs = 128, 16, 8, 16
         lens = [700, 33, 1, 1500, 129]
@@ -163,7 +181,7 @@ def _run_world(world):
     for r in range(world):
         bad = [k for k, ok in got[r].items() if not ok]
         assert not bad, f"rank {r} of {world}: {bad}"
-        assert len(got[r]) == 18
+        assert len(got[r]) == 19
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
