@@ -365,6 +365,13 @@ const char* flash_attn_version(void);
 int flash_attn_device_status(void);
 int flash_attn_release_workspaces(void);
 /*
+ *   flash_attn_debug_launch_rank : the host copy of the index arithmetic that orders the rows of a
+ *                               head-sharded prefill grid (which band of tile pairs, by weight, grid row
+ *                               `grid_row` runs when the first `first_wave_rows` rows take every
+ *                               `stride`-th band); exists so that the mapping can be checked on the CPU.
+ */
+int flash_attn_debug_launch_rank(int grid_row, int first_wave_rows, int stride);
+/*
  *   flash_attn_debug_read     : builds with -DFA_TRACE only (returns -1 otherwise): copies up to
  *                               `bytes` (max 65536) of the current device's debug area to host
  *                               memory: int status word at byte 0; from byte 256, when the option

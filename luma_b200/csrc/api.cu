@@ -506,6 +506,10 @@ int flash_attn_debug_read(void* dst, int bytes) {
 
 int flash_attn_release_workspaces(void) { return fa::release_workspaces(); }
 
+int flash_attn_debug_launch_rank(int grid_row, int first_wave_rows, int stride) {
+    return fa::launch_rank(grid_row, first_wave_rows, stride);
+}
+
 int flash_attn_set_option(const char* name, int value) {
     if (name == nullptr) return 1;
     if (std::strcmp(name, "force_generic") == 0) {

@@ -108,6 +108,18 @@ __device__ __forceinline__ int block_slot(const int* __restrict__ block_tables, 
     return block_tables[s * max_blocks + logical_block] * block_size + offset;
 }
 
+// Launch order of the rows (blockIdx.y) of a head-sharded tensor-core prefill grid: row `by` of the grid
+// runs the band of tile pairs with this rank by weight (0 = heaviest). w == 0: heaviest first. Otherwise
+// the first w rows of the grid are every m-th rank (0, m, 2m, ...: a first wave that mixes all weights),
+// the ranks in between follow in ascending order, and ranks from w * m on keep their place. A bijection
+// of [0, rows) for every rows >= w * m, m >= 2.
+__host__ __device__ inline int launch_rank(int by, int w, int m) {
+    if (w <= 0) return by;
+    if (by < w) return by * m;
+    if (by - w < w * (m - 1)) return ((by - w) / (m - 1)) * m + 1 + (by - w) % (m - 1);
+    return by;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }

@@ -507,13 +507,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int num_mb = (sq.q_len + kBlockM - 1) / kBlockM;
     const int kvh = stream_id % a.kv_heads;
     const int b = stream_id / a.kv_heads;
-    int rank_y = (int)blockIdx.y;   // this row's rank by weight, 0 = heaviest
-    if (a.spread_w > 0) {
-        const int by = (int)blockIdx.y, w = a.spread_w, m = a.spread_m;
-        if (by < w) rank_y = by * m;
-        else if (by - w < w * (m - 1)) rank_y = ((by - w) / (m - 1)) * m + 1 + (by - w) % (m - 1);
-        // (rows past w * m keep their index: by - w + w * (m - 1) + ... = by)
-    }
+    const int rank_y = launch_rank((int)blockIdx.y, a.spread_w, a.spread_m);   // this row's rank by weight, 0 = heaviest
     const int pair = ((int)gridDim.y - 1 - rank_y) * a.band + (a.band - 1 - (int)(blockIdx.x % a.band));
 
     const TileInfo t0 = tile_info(sq, pair, 0, kvh, group, num_mb);

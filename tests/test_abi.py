@@ -143,3 +143,21 @@ def test_compute_without_device_fails_loudly():
         pytest.skip("a CUDA device is present")
     assert _batch() == 5
     assert "no CPU fallback" in ffi.last_error()
+
+
+def test_head_sharded_launch_order_is_a_permutation():
+    """The grid rows of a head-sharded prefill run the bands of tile pairs in another order than
+    heaviest-first (a first wave that mixes all weights, then heaviest first): the index arithmetic,
+    shared by the kernel and this host entry point, must hit every band exactly once."""
+    rank = ffi.lib.flash_attn_debug_launch_rank
+    for rows in (2, 5, 7, 10, 64, 65, 128, 1000):
+        for w in (1, 2, 3, 5, 19, 32, 148):
+            m = rows // w
+            if m < 2:
+                continue                                   # the launcher keeps heaviest-first then
+            got = [rank(by, w, m) for by in range(rows)]
+            assert sorted(got) == list(range(rows)), (rows, w, m)
+            assert got[:w] == [i * m for i in range(w)]   # the first wave samples every m-th band
+            rest = got[w:]
+            assert rest == sorted(rest)                    # the others follow heaviest first
+        assert [rank(by, 0, 0) for by in range(rows)] == list(range(rows))
