@@ -134,6 +134,34 @@ class _HostPipe:
 _host_pipes = {}
 
 
+def _host_steps(b: int, sq: int, rows: int):
+    """The (batch element, first row, end row) steps of the host pipeline. Every step is `rows` query
+    rows, except that the very first step and the very last one are cut into quarters and a half: the
+    link idles while the first chunk travels in before any kernel can run, and again while the last
+    result travels back after the last kernel, so those two are made short."""
+    steps = [(i, r0, min(sq, r0 + rows)) for i in range(b) for r0 in range(0, sq, rows)]
+    if rows >= 512 and len(steps) >= 1:
+        def cut(step, parts):
+            i, r0, r1 = step
+            n = r1 - r0
+            out, at = [], r0
+            for frac in parts:
+                size = max(128, int(n * frac) // 128 * 128)
+                end = min(r1, at + size)
+                if end > at:
+                    out.append((i, at, end))
+                at = end
+            if at < r1:
+                out.append((i, at, r1))
+            return out
+        first = cut(steps[0], (0.25, 0.25, 0.5))
+        if len(steps) == 1:
+            steps = cut(steps[0], (0.125, 0.125, 0.25, 0.25, 0.125, 0.125))
+        else:
+            steps = first + steps[1:-1] + cut(steps[-1], (0.5, 0.25, 0.25))
+    return steps
+
+
 def _host_chunk_rows(sq: int) -> int:
     """Query rows per pipeline step: a quarter of the sequence, in whole 128-row tiles, at least 1024."""
     if sq < 4096:
@@ -200,45 +228,47 @@ def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = Non
     pipe.s_in.wait_event(start)
     last = None
     step = 0
-    for i in range(b):
+    kv_have = 0
+    cur_elem = -1
+    for i, r0, r1 in _host_steps(b, sq, rows):
         kv = kv_slots[i & 1]
-        if kv["ran"] is not None:          # the last kernel that read this K/V buffer
-            pipe.s_in.wait_event(kv["ran"])
-        kv_have = 0                        # K/V rows of this batch element already on the device
-        for r0 in range(0, sq, rows):
-            r1 = min(sq, r0 + rows)
-            kv_need = min(skv, start_pos + r1)     # the chunk's rows see keys < start_pos + r1
-            sl = row_slots[step & 1]
-            step += 1
-            if sl["ran"] is not None:      # the slot's q is free once its previous kernel has run
-                pipe.s_in.wait_event(sl["ran"])
-            with torch.cuda.stream(pipe.s_in):
-                sl["q"][:, :r1 - r0].copy_(q[i:i + 1, r0:r1], non_blocking=True)
-                if kv_need > kv_have:
-                    kv["k"][:, kv_have:kv_need].copy_(k[i:i + 1, kv_have:kv_need], non_blocking=True)
-                    kv["v"][:, kv_have:kv_need].copy_(v[i:i + 1, kv_have:kv_need], non_blocking=True)
-                    kv_have = kv_need
-                arrived = torch.cuda.Event()
-                arrived.record(pipe.s_in)
-            pipe.s_run.wait_event(arrived)
-            if sl["out"] is not None:      # the slot's o is free once it has been copied back
-                pipe.s_run.wait_event(sl["out"])
-            if kv_need > 0:
-                low.flash_attn(sl["q"], kv["k"], kv["v"], sl["o"], 1, r1 - r0, kv_need, hq, hkv, d, int(start_pos) + r0,
-                               scale, None, pipe.s_run, None)
-            else:
-                with torch.cuda.stream(pipe.s_run):
-                    sl["o"].zero_()        # no key at all: the rows output zeros
-            ran = torch.cuda.Event()
-            ran.record(pipe.s_run)
-            sl["ran"] = ran
-            kv["ran"] = ran
-            pipe.s_out.wait_event(ran)
-            with torch.cuda.stream(pipe.s_out):
-                out[i:i + 1, r0:r1].copy_(sl["o"][:, :r1 - r0], non_blocking=True)
-                sl["out"] = torch.cuda.Event()
-                sl["out"].record(pipe.s_out)
-            last = sl["out"]
+        if i != cur_elem:                  # a new batch element: its K/V buffer must be free, nothing of it is on the device yet
+            cur_elem = i
+            kv_have = 0
+            if kv["ran"] is not None:      # the last kernel that read this K/V buffer
+                pipe.s_in.wait_event(kv["ran"])
+        kv_need = min(skv, start_pos + r1)     # the chunk's rows see keys < start_pos + r1
+        sl = row_slots[step & 1]
+        step += 1
+        if sl["ran"] is not None:      # the slot's q is free once its previous kernel has run
+            pipe.s_in.wait_event(sl["ran"])
+        with torch.cuda.stream(pipe.s_in):
+            sl["q"][:, :r1 - r0].copy_(q[i:i + 1, r0:r1], non_blocking=True)
+            if kv_need > kv_have:
+                kv["k"][:, kv_have:kv_need].copy_(k[i:i + 1, kv_have:kv_need], non_blocking=True)
+                kv["v"][:, kv_have:kv_need].copy_(v[i:i + 1, kv_have:kv_need], non_blocking=True)
+                kv_have = kv_need
+            arrived = torch.cuda.Event()
+            arrived.record(pipe.s_in)
+        pipe.s_run.wait_event(arrived)
+        if sl["out"] is not None:      # the slot's o is free once it has been copied back
+            pipe.s_run.wait_event(sl["out"])
+        if kv_need > 0:
+            low.flash_attn(sl["q"], kv["k"], kv["v"], sl["o"], 1, r1 - r0, kv_need, hq, hkv, d, int(start_pos) + r0,
+                           scale, None, pipe.s_run, None)
+        else:
+            with torch.cuda.stream(pipe.s_run):
+                sl["o"].zero_()        # no key at all: the rows output zeros
+        ran = torch.cuda.Event()
+        ran.record(pipe.s_run)
+        sl["ran"] = ran
+        kv["ran"] = ran
+        pipe.s_out.wait_event(ran)
+        with torch.cuda.stream(pipe.s_out):
+            out[i:i + 1, r0:r1].copy_(sl["o"][:, :r1 - r0], non_blocking=True)
+            sl["out"] = torch.cuda.Event()
+            sl["out"].record(pipe.s_out)
+        last = sl["out"]
     if last is not None:
         cur.wait_event(last)
     return out
