@@ -336,6 +336,8 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *                             3 = log {start ns, end ns, SM id} of up to 2048 CTAs from byte 16384
  *       "prefill_trace_y"     blockIdx.y of the CTA whose timeline is recorded (0 = heaviest)
  *       "prefill_band"        tile pairs of one K/V stream launched next to each other (0 = automatic)
+ *       "prefill_groups"      groups of K/V streams the prefill grid runs one after the other (0 = automatic:
+ *                             about 16 MiB of K/V per group when no launch band shares them)
  *       "prefill_order"       1 = heaviest-first launch order also for head-sharded calls (0 = their first wave mixes all weights)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  *       "prefill_wait_us"     bound of every wait inside the tcgen05 prefill kernel, microseconds

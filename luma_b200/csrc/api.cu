@@ -27,6 +27,7 @@ std::atomic<int> g_prefill_trace{0};
 std::atomic<int> g_prefill_trace_y{0};
 std::atomic<int> g_prefill_band{0};
 std::atomic<int> g_prefill_order{0};
+std::atomic<int> g_prefill_groups{0};
 std::atomic<int> g_prefill_wait_us{0};
 std::atomic<int> g_prefill_test_skip_k{0};
 }  // namespace
@@ -50,6 +51,7 @@ int get_option_decode_chunk() { return g_decode_chunk.load(std::memory_order_rel
 int get_option_prefill_trace() { return g_prefill_trace.load(std::memory_order_relaxed); }
 int get_option_prefill_trace_y() { return g_prefill_trace_y.load(std::memory_order_relaxed); }
 int get_option_prefill_band() { return g_prefill_band.load(std::memory_order_relaxed); }
+int get_option_prefill_groups() { return g_prefill_groups.load(std::memory_order_relaxed); }
 int get_option_prefill_order() { return g_prefill_order.load(std::memory_order_relaxed); }
 int get_option_prefill_wait_us() { return g_prefill_wait_us.load(std::memory_order_relaxed); }
 int get_option_prefill_test_skip_k() { return g_prefill_test_skip_k.load(std::memory_order_relaxed); }
@@ -518,6 +520,10 @@ int flash_attn_set_option(const char* name, int value) {
     }
     if (std::strcmp(name, "prefill_trace") == 0) {
         fa::g_prefill_trace = value;
+        return 0;
+    }
+    if (std::strcmp(name, "prefill_groups") == 0) {
+        fa::g_prefill_groups = value;
         return 0;
     }
     if (std::strcmp(name, "prefill_order") == 0) {

@@ -141,6 +141,7 @@ int get_option_decode_chunk();
 int get_option_prefill_trace();
 int get_option_prefill_trace_y();
 int get_option_prefill_band();
+int get_option_prefill_groups();        // groups of K/V streams the tensor-core prefill grid runs one after the other (0 = automatic)
 int get_option_prefill_order();         // 1 = heaviest-first launch order even for head-sharded calls (0 = the default)
 int get_option_prefill_wait_us();       // bound of the tcgen05 kernel's waits in microseconds (0 = the default, 2 s)
 int get_option_prefill_test_skip_k();   // test hook: 1 + index of a K tile the producer never requests (0 = off)
