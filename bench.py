@@ -19,6 +19,10 @@ At every N the run also checks, outside the timed region, what the timed calls p
 bit for bit with what arrived in its gathered output; at N = 1 a slice is recomputed on the library's
 independent SIMT kernel.
 
+Beside the CPU baseline the line carries "reference_cuda": the reference's own CUDA kernels (compiled
+unmodified for sm_100a into oracle/_ref where the reference tree was mounted at build time), device-timed
+on the S=8192 prefill and the batch-64 decode, outside the timed region, as a second stated baseline.
+
 `--impl reference` times the CPU restatement of luma-cpu's math-path attention (oracle/) on the
 host cores, on the same workload definition: the reference's own implementation of this path is
 Rust and cannot be built with this image's toolchains.
@@ -719,6 +723,69 @@ def cpu_baseline_prefill(name, budget_s=12.0):
             "sample": cpu_sample_text(name, nh) + f"; {sec:.2f} s"}
 
 
+def reference_cuda_baseline(torch, low, ffi, dev):
+    """The reference's own CUDA kernels (luma-flash-attn/kernels/*.cu, compiled unmodified for sm_100a
+    into oracle/_ref by oracle/Makefile's `ref` target) on the S=8192 GQA prefill and the batch-64 paged
+    decode, device-timed, with their outputs compared with this library's. Part of the baseline leg: a
+    second stated baseline beside the CPU one, not a measured product path. None where the file was not
+    built (the reference tree is not mounted everywhere)."""
+    import ctypes
+    path = ROOT / "oracle" / "_ref" / "libflash_attn_ref.so"
+    if not path.exists():
+        return None
+    ref = ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
+    ref.flash_attn_bf16.argtypes = ffi._BATCH_ARGS
+    ref.flash_attn_with_kvcache_bf16.argtypes = ffi._KVCACHE_ARGS
+    st = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3 / reps
+
+    out = {"kind": "reference CUDA kernels compiled for sm_100a"}
+    b, hq, hkv, s, d, seed, scale_in, _lse = PREFILL["prefill_c3"]
+    q, k, v = make_prefill(torch, dev, b, hq, hkv, s, d, seed, scale_in)
+    theirs, mine = torch.empty_like(q), torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+
+    def ref_prefill():
+        rc = ref.flash_attn_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), theirs.data_ptr(), b, s, s, hq, hkv, d, 0, scale, None, st)
+        if rc != 0:
+            raise RuntimeError(f"reference flash_attn_bf16 returned {rc}")
+    sec = timed(ref_prefill, 2)
+    low.flash_attn(q, k, v, mine, b, s, s, hq, hkv, d, 0, scale)
+    torch.cuda.synchronize()
+    diff = float((mine.float() - theirs.float()).abs().max())
+    out["prefill_c3"] = {"value": causal_flops(b, hq, s, s, d) / sec / 1e12, "unit": "TFLOP/s", "ms": sec * 1e3, "max_abs_diff_vs_ours": diff}
+    del q, k, v, theirs, mine
+    torch.cuda.empty_cache()
+
+    batch, hq, hkv, d, page, lo, hi, pool, seed = DECODE["decode_c4"]
+    q, kc, vc, lens_d, table_d, lens = make_decode(torch, dev, batch, hq, hkv, d, page, lo, hi, pool, seed)
+    theirs, mine = torch.empty_like(q), torch.empty_like(q)
+
+    def ref_decode():
+        rc = ref.flash_attn_with_kvcache_bf16(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), theirs.data_ptr(), table_d.data_ptr(),
+                                              lens_d.data_ptr(), batch, 1, hq, hkv, d, page, table_d.shape[1], scale, st)
+        if rc != 0:
+            raise RuntimeError(f"reference flash_attn_with_kvcache_bf16 returned {rc}")
+    sec = timed(ref_decode, 3)
+    low.flash_attn_with_kvcache(q, kc, vc, mine, table_d, lens_d, batch, 1, hq, hkv, d, page, table_d.shape[1], scale)
+    torch.cuda.synchronize()
+    diff = float((mine.float() - theirs.float()).abs().max())
+    out["decode_c4"] = {"value": decode_bytes(lens, hq, hkv, d, page) / sec / 1e9, "unit": "GB/s", "ms": sec * 1e3, "max_abs_diff_vs_ours": diff}
+    del q, kc, vc, theirs, mine
+    torch.cuda.empty_cache()
+    return out
+
+
 def reference_arm(args):
     """`--impl reference`: the CPU path on the host cores, K timed steps after W warm-up steps as
     given, each step a bounded sample of the same headline workload as the GPU arm at this N."""
@@ -893,8 +960,10 @@ def main():
 
     # ---- CPU baseline, rank 0, N == 1 only -----------------------------------------------------
     cpu = None
+    ref_cuda = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline_prefill("prefill_c3")
+        ref_cuda = reference_cuda_baseline(torch, low, ffi, dev)
 
     if rank == 0:
         line = {
@@ -911,6 +980,8 @@ def main():
             line["gather"] = primary["gather"]
         if "per_gpu" in primary:
             line["per_gpu"] = primary["per_gpu"]
+        if ref_cuda is not None:
+            line["reference_cuda"] = ref_cuda
         if numa:
             line["host_cpus"] = numa
         print(json.dumps(line))
