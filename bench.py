@@ -676,10 +676,34 @@ def run_e2e(torch, dev, dist, q, k, v, flops_total, steps):
     barrier = (lambda: dist.barrier()) if dist is not None else None
     sec = _max_over_ranks(torch, dist, dev, time_steps(torch, e2e_step, steps, 2, barrier))
     ok = bool(torch.isfinite(ho.float()).all())
+    h2d_bytes, d2h_bytes = int((q.numel() + k.numel() + v.numel()) * 2), int(q.numel() * 2)
+
+    # What the host link gives while every rank uses it at once, both directions together: the same
+    # bytes as plain copies on two streams, no kernel. The e2e step cannot be shorter than this.
+    dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def link_step():
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            dq.copy_(hq_h, non_blocking=True)
+            dk.copy_(hk_h, non_blocking=True)
+            dv.copy_(hv_h, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            ho.copy_(q, non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+
+    link_sec = _max_over_ranks(torch, dist, dev, time_steps(torch, link_step, 3, 1, barrier)) / 3
+    del dq, dk, dv
     return {"value": flops_total * steps / sec / 1e12, "unit": "TFLOP/s",
-            "h2d_bytes_per_step": int((q.numel() + k.numel() + v.numel()) * 2), "d2h_bytes_per_step": int(q.numel() * 2),
+            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
             "steps": steps, "ms_per_step": sec / steps * 1e3, "finite": ok,
-            "api": "high.flash_attn_func_host (pinned host in/out, row chunks pipelined over 3 streams); bytes per GPU"}
+            "host_link": {"copies_only_ms": link_sec * 1e3, "gbs_per_gpu": (h2d_bytes + d2h_bytes) / link_sec / 1e9,
+                          "frac": link_sec / (sec / steps)},
+            "api": "high.flash_attn_func_host -> flash_attn_host_bf16 (pinned host in/out, row chunks pipelined over 3 streams); bytes per GPU"}
 
 
 # ------------------------------------------------------------------------------------------

@@ -323,6 +323,38 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
                                    int block_size, int max_blocks, float scale, void* stream);
 
 /*
+ * Batched causal attention for tensors in HOST memory: q (batch, q_seq_len, q_num_heads, head_size),
+ * k/v (batch, kv_seq_len, kv_num_heads, head_size) and o like q, dense row-major, page-locked for
+ * the copies to be asynchronous. No counterpart in the reference (its callers hold device tensors,
+ * luma-flash-attn/src/api/high.rs:157-290); this is the call the end-to-end figure of the benchmark
+ * goes through. The work is cut into steps of one batch element and `chunk_rows` query rows (0 =
+ * automatic: half of the sequence, the first and last step cut finer) and pipelined over three
+ * streams of `device`: each chunk travels in with the K/V rows up to its own end (a chunked prefill
+ * with start_pos advanced per chunk), runs through flash_attn_<T>, and travels out while the next
+ * ones are in flight. Staging buffers are kept per device (two row slots, two K/V slots of the
+ * largest shape seen) and freed by flash_attn_release_workspaces. `stream` is the caller's stream
+ * on `device`: the pipeline starts after the work already in it and the stream continues when the
+ * last row of o has reached the host. Check order: NULL -> NULL_PTR; non-positive sizes or
+ * Hq % Hkv -> INVALID_SHAPE; start_pos < 0 -> INVALID_START_POS; head_size not in {32,64,128} ->
+ * INVALID_HEAD_SIZE; CUDA failures -> CUDA.
+ *   flash_attn_host_steps : the (batch element, first row, end row) triples such a call is cut
+ *                           into, written to steps_out (3 ints each, up to `capacity` triples);
+ *                           returns their number. Host arithmetic only.
+ */
+int flash_attn_host_f32(const float* q, const float* k, const float* v, float* o,
+                        int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                        int head_size, int start_pos, float scale, int device, int chunk_rows, void* stream);
+int flash_attn_host_f16(const flash_attn_f16_t* q, const flash_attn_f16_t* k, const flash_attn_f16_t* v,
+                        flash_attn_f16_t* o,
+                        int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                        int head_size, int start_pos, float scale, int device, int chunk_rows, void* stream);
+int flash_attn_host_bf16(const flash_attn_bf16_t* q, const flash_attn_bf16_t* k, const flash_attn_bf16_t* v,
+                         flash_attn_bf16_t* o,
+                         int batch, int q_seq_len, int kv_seq_len, int q_num_heads, int kv_num_heads,
+                         int head_size, int start_pos, float scale, int device, int chunk_rows, void* stream);
+int flash_attn_host_steps(int batch, int q_seq_len, int chunk_rows, int* steps_out, int capacity);
+
+/*
  * Tuning and introspection. No counterpart in the reference.
  *   flash_attn_version        : library version string.
  *   flash_attn_last_path      : name of the kernel family the last successful call on this
@@ -360,7 +392,7 @@ int flash_attn_decode_bf16_noalloc(const flash_attn_bf16_t* q, const flash_attn_
  *                               word. 0 = healthy, non-zero = the code of an expired wait,
  *                               -1 = no device / not readable.
  *   flash_attn_release_workspaces : releases (stream-ordered) every split-K workspace the decode
- *                               path holds; returns how many there were. The library keeps at most
+ *                               path holds and the staging buffers of flash_attn_host_<T>; returns how many there were. The library keeps at most
  *                               32 of them (one per device and stream, least recently used first out).
  */
 const char* flash_attn_version(void);

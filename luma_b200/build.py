@@ -25,7 +25,7 @@ LIB_PATH = LIB_DIR / "libflash_attn.so"
 
 ARCHIVE_PATH = LIB_DIR / "libflash_attn.a"
 
-SOURCES = ["api.cu", "tile_simt.cu", "decode_splitk.cu", "prefill_tcgen05.cu", "kv_append.cu", "softmax_lastdim.cu", "comm.cu"]
+SOURCES = ["api.cu", "tile_simt.cu", "decode_splitk.cu", "prefill_tcgen05.cu", "kv_append.cu", "softmax_lastdim.cu", "comm.cu", "host_pipe.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -506,7 +506,7 @@ int flash_attn_debug_read(void* dst, int bytes) {
     return fa::prefill_debug_read(dst, bytes);
 }
 
-int flash_attn_release_workspaces(void) { return fa::release_workspaces(); }
+int flash_attn_release_workspaces(void) { return fa::release_workspaces() + fa::release_host_pipes(); }
 
 int flash_attn_debug_launch_rank(int grid_row, int first_wave_rows, int stride) {
     return fa::launch_rank(grid_row, first_wave_rows, stride);

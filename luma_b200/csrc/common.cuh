@@ -133,6 +133,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 // ---- host side -------------------------------------------------------------------------
 
+int release_host_pipes();   // host_pipe.cu: frees the staging buffers of flash_attn_host_<T>; returns how many devices held some
 void set_last_error(const char* msg);
 void set_last_errorf(const char* fmt, ...);
 void note_path(const char* name, int launches);   // records flash_attn_last_path / _launches

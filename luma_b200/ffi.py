@@ -45,7 +45,8 @@ EXPORTED_SYMBOLS = (
        "flash_attn_f16_allgather_multicast", "flash_attn_bf16_allgather_multicast",
        "flash_attn_with_kvcache_f16_allgather", "flash_attn_with_kvcache_bf16_allgather",
        "flash_attn_kvcache_append", "flash_attn_varlen_f16_total", "flash_attn_varlen_bf16_total",
-       "flash_attn_release_workspaces", "flash_attn_debug_launch_rank"]
+       "flash_attn_release_workspaces", "flash_attn_debug_launch_rank", "flash_attn_host_steps"]
+    + [f"flash_attn_host_{s}" for s in DTYPE_SUFFIX]
     + [f"luma_softmax_{s}" for s in DTYPE_SUFFIX]   # include/luma_nn_kernels.h
     + ["flash_attn_debug_block_slots", "flash_attn_version", "flash_attn_device_status", "flash_attn_debug_read", "flash_attn_last_path",
        "flash_attn_last_launches", "flash_attn_set_option"]
@@ -96,6 +97,12 @@ for _s in ("f16", "bf16"):
     getattr(lib, f"flash_attn_with_kvcache_{_s}_allgather").restype = c_int
 lib.flash_attn_debug_launch_rank.argtypes = [c_int, c_int, c_int]
 lib.flash_attn_debug_launch_rank.restype = c_int
+_HOST_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
+for _s in DTYPE_SUFFIX:
+    getattr(lib, f"flash_attn_host_{_s}").argtypes = _HOST_ARGS
+    getattr(lib, f"flash_attn_host_{_s}").restype = c_int
+lib.flash_attn_host_steps.argtypes = [c_int, c_int, c_int, c_void_p, c_int]
+lib.flash_attn_host_steps.restype = c_int
 lib.flash_attn_release_workspaces.argtypes = []
 lib.flash_attn_release_workspaces.restype = c_int
 lib.luma_comm_unique_id.argtypes = [c_void_p]

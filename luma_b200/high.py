@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from . import error as E
-from . import low
+from . import ffi, low
 
 
 def _check_float(t: torch.Tensor, what: str) -> None:
@@ -111,62 +111,13 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens, block_table,
     return o
 
 
-class _HostPipe:
-    """Streams and device staging buffers of `flash_attn_func_host`, kept per device."""
-
-    def __init__(self, device):
-        self.device = device
-        self.s_in = torch.cuda.Stream(device)
-        self.s_run = torch.cuda.Stream(device)
-        self.s_out = torch.cuda.Stream(device)
-        self.key = None
-        self.kv = []      # two (k, v) device buffers: batch elements alternate
-        self.rows = []    # two (q chunk, o chunk) device buffers: row chunks alternate
-
-    def buffers(self, key, make_kv, make_rows):
-        if self.key != key:
-            self.kv = [make_kv() for _ in range(2)]
-            self.rows = [make_rows() for _ in range(2)]
-            self.key = key
-        return self.kv, self.rows
-
-
-_host_pipes = {}
-
-
-def _host_steps(b: int, sq: int, rows: int):
-    """The (batch element, first row, end row) steps of the host pipeline. Every step is `rows` query
-    rows, except that the very first step and the very last one are cut into quarters and a half: the
-    link idles while the first chunk travels in before any kernel can run, and again while the last
-    result travels back after the last kernel, so those two are made short."""
-    steps = [(i, r0, min(sq, r0 + rows)) for i in range(b) for r0 in range(0, sq, rows)]
-    if rows >= 512 and len(steps) >= 1:
-        def cut(step, parts):
-            i, r0, r1 = step
-            n = r1 - r0
-            out, at = [], r0
-            for frac in parts:
-                size = max(128, int(n * frac) // 128 * 128)
-                end = min(r1, at + size)
-                if end > at:
-                    out.append((i, at, end))
-                at = end
-            if at < r1:
-                out.append((i, at, r1))
-            return out
-        first = cut(steps[0], (0.25, 0.25, 0.5))
-        if len(steps) == 1:
-            steps = cut(steps[0], (0.125, 0.125, 0.25, 0.25, 0.125, 0.125))
-        else:
-            steps = first + steps[1:-1] + cut(steps[-1], (0.5, 0.25, 0.25))
-    return steps
-
-
-def _host_chunk_rows(sq: int) -> int:
-    """Query rows per pipeline step: a quarter of the sequence, in whole 128-row tiles, at least 1024."""
-    if sq < 4096:
-        return sq
-    return max(1024, ((sq + 3) // 4 + 127) // 128 * 128)
+def host_steps(b: int, sq: int, chunk_rows: int = 0):
+    """The (batch element, first row, end row) steps `flash_attn_func_host` cuts a call into."""
+    import numpy as np
+    n = ffi.lib.flash_attn_host_steps(b, sq, int(chunk_rows), None, 0)
+    buf = np.zeros((max(n, 1), 3), dtype=np.int32)
+    ffi.lib.flash_attn_host_steps(b, sq, int(chunk_rows), buf.ctypes.data, n)
+    return [tuple(int(x) for x in row) for row in buf[:n]]
 
 
 def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = None, causal: bool = True,
@@ -174,13 +125,14 @@ def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = Non
     """Batched attention for HOST tensors (this library's addition; luma has no counterpart).
 
     q (B, Sq, Hq, d), k, v (B, Skv, Hkv, d) in (preferably pinned) host memory -> `out` (B, Sq, Hq, d)
-    in host memory (allocated pinned when None). The work is cut into steps of one batch element and
-    `chunk_rows` query rows (a chunked prefill: the rows of a chunk see the keys up to their own
-    position, so a chunk needs only the K/V rows up to its end, which travel with it) and the steps are
-    pipelined over three streams: while one chunk is in the kernel, the next chunk's q rows and K/V rows
-    are on their way to the device and the previous chunk's result on its way back, which keeps both
-    directions of the host link busy instead of using them in turn. The caller's current stream
-    waits for the last copy; `out` is complete when that stream has caught up.
+    in host memory (allocated pinned when None). The library's `flash_attn_host_<T>` does the work: it
+    is cut into steps of one batch element and `chunk_rows` query rows (a chunked prefill: the rows of
+    a chunk see the keys up to their own position, so a chunk needs only the K/V rows up to its end,
+    which travel with it) and the steps are pipelined over three streams: while one chunk is in the
+    kernel, the next chunk's q rows and K/V rows are on their way to the device and the previous
+    chunk's result on its way back, which keeps both directions of the host link busy instead of using
+    them in turn. The caller's current stream waits for the last copy; `out` is complete when that
+    stream has caught up.
     """
     if not causal:
         raise E.Unsupported("flash_attn_func_host: non-causal is not supported yet (kernels are causal-only)")
@@ -205,70 +157,7 @@ def flash_attn_func_host(q, k, v, out=None, softmax_scale: Optional[float] = Non
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
     elif out.is_cuda or tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
         raise E.InvalidShape("flash_attn_func_host: out must be a contiguous host tensor shaped and typed like q")
-    rows = int(chunk_rows) if chunk_rows else _host_chunk_rows(sq)
-    rows = max(1, min(rows, sq))
-
-    pipe = _host_pipes.get(dev)
-    if pipe is None:
-        pipe = _host_pipes[dev] = _HostPipe(dev)
-    key = (sq, skv, hq, hkv, d, q.dtype, rows)
-
-    def make_kv():
-        return {"k": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev),
-                "v": torch.empty((1, skv, hkv, d), dtype=q.dtype, device=dev), "ran": None}
-
-    def make_rows():
-        return {"q": torch.empty((1, rows, hq, d), dtype=q.dtype, device=dev),
-                "o": torch.empty((1, rows, hq, d), dtype=q.dtype, device=dev), "ran": None, "out": None}
-
-    kv_slots, row_slots = pipe.buffers(key, make_kv, make_rows)
-    cur = torch.cuda.current_stream(dev)
-    start = torch.cuda.Event()
-    start.record(cur)
-    pipe.s_in.wait_event(start)
-    last = None
-    step = 0
-    kv_have = 0
-    cur_elem = -1
-    for i, r0, r1 in _host_steps(b, sq, rows):
-        kv = kv_slots[i & 1]
-        if i != cur_elem:                  # a new batch element: its K/V buffer must be free, nothing of it is on the device yet
-            cur_elem = i
-            kv_have = 0
-            if kv["ran"] is not None:      # the last kernel that read this K/V buffer
-                pipe.s_in.wait_event(kv["ran"])
-        kv_need = min(skv, start_pos + r1)     # the chunk's rows see keys < start_pos + r1
-        sl = row_slots[step & 1]
-        step += 1
-        if sl["ran"] is not None:      # the slot's q is free once its previous kernel has run
-            pipe.s_in.wait_event(sl["ran"])
-        with torch.cuda.stream(pipe.s_in):
-            sl["q"][:, :r1 - r0].copy_(q[i:i + 1, r0:r1], non_blocking=True)
-            if kv_need > kv_have:
-                kv["k"][:, kv_have:kv_need].copy_(k[i:i + 1, kv_have:kv_need], non_blocking=True)
-                kv["v"][:, kv_have:kv_need].copy_(v[i:i + 1, kv_have:kv_need], non_blocking=True)
-                kv_have = kv_need
-            arrived = torch.cuda.Event()
-            arrived.record(pipe.s_in)
-        pipe.s_run.wait_event(arrived)
-        if sl["out"] is not None:      # the slot's o is free once it has been copied back
-            pipe.s_run.wait_event(sl["out"])
-        if kv_need > 0:
-            low.flash_attn(sl["q"], kv["k"], kv["v"], sl["o"], 1, r1 - r0, kv_need, hq, hkv, d, int(start_pos) + r0,
-                           scale, None, pipe.s_run, None)
-        else:
-            with torch.cuda.stream(pipe.s_run):
-                sl["o"].zero_()        # no key at all: the rows output zeros
-        ran = torch.cuda.Event()
-        ran.record(pipe.s_run)
-        sl["ran"] = ran
-        kv["ran"] = ran
-        pipe.s_out.wait_event(ran)
-        with torch.cuda.stream(pipe.s_out):
-            out[i:i + 1, r0:r1].copy_(sl["o"][:, :r1 - r0], non_blocking=True)
-            sl["out"] = torch.cuda.Event()
-            sl["out"].record(pipe.s_out)
-        last = sl["out"]
-    if last is not None:
-        cur.wait_event(last)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    stream = torch.cuda.current_stream(index).cuda_stream
+    low.flash_attn_host(q, k, v, out, b, sq, skv, hq, hkv, d, int(start_pos), scale, index, int(chunk_rows or 0), stream)
     return out

@@ -246,3 +246,17 @@ def softmax_last_dim(x, out=None, stream=None):
     E.from_status(code, ffi.last_error())
     return out
 
+
+
+def flash_attn_host(q, k, v, o, batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads, head_size, start_pos, scale,
+                    device_index, chunk_rows=0, stream=0):
+    """`flash_attn_host_<T>` of include/flash_attn.h: q/k/v/o are HOST tensors (pinned for asynchronous
+    copies); the library pipelines copies and kernels over its own three streams of `device_index`."""
+    sfx = _suffix(q)
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
+        if t.is_cuda:
+            raise E.Unsupported(f"flash_attn_host: {name} must be a host tensor")
+    code = getattr(ffi.lib, f"flash_attn_host_{sfx}")(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), batch, q_seq_len, kv_seq_len, q_num_heads, kv_num_heads,
+        head_size, start_pos, scale, int(device_index), int(chunk_rows), int(stream))
+    E.from_status(code, ffi.last_error())

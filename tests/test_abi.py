@@ -161,3 +161,23 @@ def test_head_sharded_launch_order_is_a_permutation():
             rest = got[w:]
             assert rest == sorted(rest)                    # the others follow heaviest first
         assert [rank(by, 0, 0) for by in range(rows)] == list(range(rows))
+
+
+def test_host_pipeline_steps_tile_every_batch_element():
+    """flash_attn_host_<T> cuts a call into (batch element, first row, end row) steps: per element they
+    must cover [0, q_seq_len) once, in order, in whole 128-row tiles except at the very end, and the
+    first and last steps of a long call are the short ones (host arithmetic only, no device)."""
+    from luma_b200 import high
+    for b, sq, rows in [(2, 8192, 0), (1, 16384, 0), (1, 8192, 0), (3, 1000, 0), (2, 8192, 1024), (1, 300, 128),
+                        (2, 4096, 0), (1, 1, 0), (4, 129, 64), (1, 5000, 0)]:
+        steps = high.host_steps(b, sq, rows)
+        assert [e for e, _, _ in steps] == sorted(e for e, _, _ in steps)
+        for e in range(b):
+            mine = [(r0, r1) for i, r0, r1 in steps if i == e]
+            assert mine[0][0] == 0 and mine[-1][1] == sq
+            assert all(a[1] == n[0] for a, n in zip(mine, mine[1:]))
+            assert all(r1 > r0 for r0, r1 in mine)
+            assert all(r0 % 128 == 0 for r0, _ in mine) or rows not in (0,) and rows % 128 != 0
+    long_call = high.host_steps(2, 8192, 0)
+    sizes = [r1 - r0 for _, r0, r1 in long_call]
+    assert sizes[0] == min(sizes) and sizes[-1] == min(sizes) and max(sizes) == 4096 and sum(sizes) == 2 * 8192

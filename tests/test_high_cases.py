@@ -134,7 +134,7 @@ def test_offset_views_are_bit_identical():
 
 
 def test_host_tensor_call_matches_device_call():
-    """flash_attn_func_host (pinned host tensors, batch elements and row chunks pipelined over three streams) gives
+    """flash_attn_func_host (pinned host tensors, batch elements and row chunks pipelined over the library's streams) gives
     the same bits as the device call, twice in a row (staging buffers and events are reused)."""
     torch.manual_seed(7)
     b, s, hq, hkv, d = 3, 300, 4, 2, 128
