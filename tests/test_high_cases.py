@@ -169,3 +169,46 @@ def test_host_tensor_call_in_row_chunks(chunk_rows, start_pos, skv):
         torch.cuda.current_stream().synchronize()
         # a chunk that starts inside a tile of the one-piece call groups the keys differently: same values, other rounding
         assert (got.float() - want).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 4e-3), (torch.float32, 2e-4)])
+def test_host_tensor_call_long_sequence_automatic_steps(dtype, tol):
+    """A sequence long enough for the automatic cut (half-sequence chunks, the first and last one in
+    pieces down to a sixteenth; K/V of the last chunk in one copy), after a smaller call, so that the
+    staging buffers grow in between; pageable (not pinned) inputs are accepted as well; the buffers
+    come back after flash_attn_release_workspaces."""
+    from luma_b200 import ffi
+    torch.manual_seed(9)
+    small = [torch.randn(1, 200, 2, 64).to(dtype) for _ in range(3)]
+    got = high.flash_attn_func_host(*small)
+    torch.cuda.current_stream().synchronize()
+    want = high.flash_attn_func(*(t.cuda() for t in small)).float().cpu()
+    assert (got.float() - want).abs().max().item() <= tol
+    b, s, hq, hkv, d = 2, 4608, 2, 1, 64
+    assert len(high.host_steps(b, s)) > 2 * b
+    q, k, v = torch.randn(b, s, hq, d).to(dtype), torch.randn(b, s, hkv, d).to(dtype), torch.randn(b, s, hkv, d).to(dtype)
+    want = high.flash_attn_func(q.cuda(), k.cuda(), v.cuda()).float().cpu()
+    for pinned in (True, False):
+        args = [t.pin_memory() for t in (q, k, v)] if pinned else [q, k, v]
+        got = high.flash_attn_func_host(*args)
+        torch.cuda.current_stream().synchronize()
+        assert (got.float() - want).abs().max().item() <= tol
+    assert ffi.lib.flash_attn_release_workspaces() >= 1
+    got = high.flash_attn_func_host(q, k, v)
+    torch.cuda.current_stream().synchronize()
+    assert (got.float() - want).abs().max().item() <= tol
+
+
+def test_host_entry_point_status_codes():
+    """flash_attn_host_<T> validates in the batched entry point's order before touching the device."""
+    from luma_b200 import ffi
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
+    f = ffi.lib.flash_attn_host_bf16
+    p = q.data_ptr()
+    assert f(None, p, p, p, 1, 8, 8, 2, 2, 64, 0, 0.125, 0, 0, None) == 1
+    assert f(p, p, p, p, 1, 0, 8, 2, 2, 64, 0, 0.125, 0, 0, None) == 2
+    assert f(p, p, p, p, 1, 8, 8, 3, 2, 64, 0, 0.125, 0, 0, None) == 2
+    assert f(p, p, p, p, 1, 8, 8, 2, 2, 64, -1, 0.125, 0, 0, None) == 4
+    assert f(p, p, p, p, 1, 8, 8, 2, 2, 48, 0, 0.125, 0, 0, None) == 3
+    assert f(p, p, p, p, 1, 8, 8, 2, 2, 64, 0, 0.125, 99, 0, None) == 5
+    assert b"no CUDA device 99" in ffi.lib.flash_attn_last_error()
