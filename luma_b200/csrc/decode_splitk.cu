@@ -142,6 +142,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_splitk_kernel(const Decode
     const int g = lane >> 2;   // mma row group
     const int c4 = lane & 3;
 
+    // A merge kernel launched with programmatic stream serialisation may take its place on the SMs as
+    // soon as every CTA of this grid has started (it still waits for this grid to finish before it reads).
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
     // KV heads vary fastest across the grid: the CTAs that read the adjacent 256-byte slices of the
     // same token rows (one slice per KV head) are launched together, which keeps DRAM pages open.
     const int kvh = blockIdx.x / a.head_blocks;
@@ -385,6 +389,9 @@ __global__ void __launch_bounds__(D) decode_merge_kernel(const float* __restrict
     const int d = threadIdx.x;
     const int L = context_lens[s];
     const int n = L > 0 ? min(max_splits, (L + chunk - 1) / chunk) : 0;
+    // the split-K grid this one depends on has finished and its partials are visible (returns at once
+    // when the launch carries no programmatic dependency)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const long long row0 = ((long long)s * q_heads + h) * max_splits;
     float mstar = -INFINITY;
     for (int i = 0; i < n; ++i) mstar = fmaxf(mstar, ws_ml[row0 + i].x);
@@ -489,7 +496,24 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         mo.o_head0 = p.o_head0;
         mo.peer0 = (p.o_head0 / p.q_heads + 1) % p.n_out;
     }
-    decode_merge_kernel<T, D><<<mgrid, D, 0, stream>>>(a.ws_acc, a.ws_ml, p.context_lens, mo, p.q_heads, chunk, max_splits);
+    {
+        // programmatic dependent launch: the merge grid is set up while the split-K grid drains
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = mgrid;
+        cfg.blockDim = dim3(D);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        const float* ws_acc = a.ws_acc;
+        const float2* ws_ml = a.ws_ml;
+        const int* lens = p.context_lens;
+        const int q_heads = p.q_heads;
+        cudaLaunchKernelEx(&cfg, decode_merge_kernel<T, D>, ws_acc, ws_ml, lens, mo, q_heads, chunk, max_splits);
+    }
     rc = check_launch("decode_merge_kernel");
     if (rc == FLASH_ATTN_OK) note_path("decode_splitk", 2);
     return rc;
