@@ -703,7 +703,7 @@ def run_e2e(torch, dev, dist, q, k, v, flops_total, steps):
             "steps": steps, "ms_per_step": sec / steps * 1e3, "finite": ok,
             "host_link": {"copies_only_ms": link_sec * 1e3, "gbs_per_gpu": (h2d_bytes + d2h_bytes) / link_sec / 1e9,
                           "frac": link_sec / (sec / steps)},
-            "api": "high.flash_attn_func_host -> flash_attn_host_bf16 (pinned host in/out, row chunks pipelined over 3 streams); bytes per GPU"}
+            "api": "high.flash_attn_func_host -> flash_attn_host_bf16 (pinned host buffers, row chunks pipelined); bytes per GPU"}
 
 
 # ------------------------------------------------------------------------------------------
@@ -722,7 +722,7 @@ def cpu_sample_inputs(name, n_heads, seed=0):
 def cpu_sample_text(name, n_heads):
     b, hq, hkv, s, _d, _seed, _sc, _lse = PREFILL[name]
     return (f"1 of {b} batch elements x 1 of {hkv} KV heads x {n_heads} of its {hq // hkv} query heads, full S={s}; "
-            "f32 math path over the full key range (oracle port of luma-cpu); rate counts causal FLOPs only")
+            "f32 math path (oracle port of luma-cpu), causal FLOPs counted")
 
 
 def cpu_baseline_prefill(name, budget_s=12.0):
@@ -848,6 +848,17 @@ def reference_arm(args):
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def _short_floats(x):
+    """Six significant digits for every float of the printed line (it has to survive in a log tail)."""
+    if isinstance(x, float):
+        return float(f"{x:.6g}")
+    if isinstance(x, dict):
+        return {k: _short_floats(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_short_floats(v) for v in x]
+    return x
 
 
 def compact(res):
@@ -1008,7 +1019,7 @@ def main():
             line["reference_cuda"] = ref_cuda
         if numa:
             line["host_cpus"] = numa
-        print(json.dumps(line))
+        print(json.dumps(_short_floats(line)))
     ok = primary["parity"]["ok"] and all(w.get("parity_ok", True) for w in workloads.values())
     if dist is not None:
         dist.barrier()
