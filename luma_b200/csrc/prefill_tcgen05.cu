@@ -724,17 +724,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     else tc_mma_ts_imm<true>(d_tmem, p_tmem + kk * 8, vd + inc, idesc_pv);
                 }
             };
-            for (int t = 0; t < 2 && alive; ++t)
-                if (ts[t].valid) alive = (mbar_wait(sm, &sm.q_full[t], 0, a, 10));
+            // The copies were requested in the order Q0, K0, Q1: the first S of tile 0 is issued as soon as
+            // its two operands are there, without waiting for the other tile's Q.
+            if (ts[0].valid) alive = (mbar_wait(sm, &sm.q_full[0], 0, a, 10));
             if (alive && n_max > 0) alive = (mbar_wait(sm, &sm.k_full[0], 0, a, 11));
+            if (alive && ts[0].n_kv > 0) {
+                tc_fence_after();
+                issue_s(0, 0);
+                tc_commit(&sm.s_full[0]);
+            }
+            if (alive && ts[1].valid) alive = (mbar_wait(sm, &sm.q_full[1], 0, a, 10));
             FA_TRACE_EVENT(2, kTraceSteps - 1, 2);       // Q and the first K tile have landed
             if (alive && n_max > 0) {
                 tc_fence_after();
-                for (int t = 0; t < 2; ++t) {
-                    if (ts[t].n_kv > 0) {
-                        issue_s(t, 0);
-                        tc_commit(&sm.s_full[t]);
-                    }
+                if (ts[1].n_kv > 0) {
+                    issue_s(1, 0);
+                    tc_commit(&sm.s_full[1]);
                 }
                 tc_commit(&sm.k_empty[0]);
             }
