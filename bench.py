@@ -53,7 +53,7 @@ NOMINAL_NVLINK_GBS = 900.0
 # GPU processes its share of the heads; q, k, v and o shard with them). The decode figure is the ratio
 # measured on decode_c4_small (397.9 MB moved for 394.2 MB of algorithmic bytes, L2 hit rate 0.1 %:
 # traffic grows in proportion to the cached tokens) applied to the run's own bytes.
-NCU_TRAFFIC_BYTES = {"prefill_c2": 201_468_672 + 49_486_080, "prefill_c3": 381_323_520 + 99_673_856,
+NCU_TRAFFIC_BYTES = {"prefill_c2": 201_468_672 + 49_486_080, "prefill_c3": 202_012_928 + 101_843_968,
                      "prefill_c5": 666_307_840 + 230_259_968}
 NCU_DECODE_TRAFFIC_RATIO = (394_186_496 + 3_808_768) / 394_223_184
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
