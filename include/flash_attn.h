@@ -370,7 +370,7 @@ int flash_attn_host_steps(int batch, int q_seq_len, int chunk_rows, int* steps_o
  *       "prefill_band"        tile pairs of one K/V stream launched next to each other (0 = automatic)
  *       "prefill_groups"      groups of K/V streams the prefill grid runs one after the other (0 = automatic:
  *                             about 16 MiB of K/V per group when no launch band shares them, whole batch
- *                             elements of about 48 MiB of K/V per group for batched GQA calls)
+ *                             elements or sequences, about 48 MiB of K/V per group, for batched and packed GQA calls)
  *       "prefill_order"       1 = heaviest-first launch order also for head-sharded calls (0 = their first wave mixes all weights)
  *       "decode_chunk_tokens" tokens per split-K work item (0 = automatic)
  *       "prefill_wait_us"     bound of every wait inside the tcgen05 prefill kernel, microseconds

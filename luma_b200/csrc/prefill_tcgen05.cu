@@ -1410,11 +1410,14 @@ int launch_typed(const AttnParams& p, cudaStream_t stream) {
         if (get_option_prefill_groups() > 0) groups = get_option_prefill_groups();
         else if (band == 1 && pairs > 1 && p.n_out <= 1 && streams * kv_bytes_per_stream > 2 * budget)
             groups = (int)std::min<long long>(streams, (streams * kv_bytes_per_stream + budget - 1) / budget);
-        else if (band > 1 && p.n_out <= 1 && p.mode == MODE_BATCH && p.num_seqs >= 2 && streams * kv_bytes_per_stream > (48LL << 20)) {
-            // GQA launches share K/V inside a band already; running whole batch elements one after the other
-            // (about 48 MiB of K/V at a time) still keeps more of q, k, v and o in L2 and with it power for
-            // the tensor pipe: B=2, Hq=32, Hkv=8, S=8192 1235-1237 against 1223-1225 TFLOP/s.
-            const long long per_elem = (long long)p.kv_heads * kv_bytes_per_stream;
+        else if (band > 1 && p.n_out <= 1 && (p.mode == MODE_BATCH || p.mode == MODE_VARLEN) && p.num_seqs >= 2 &&
+                 streams * kv_bytes_per_stream > (48LL << 20) * (p.mode == MODE_VARLEN ? 2 : 1)) {
+            // GQA launches share K/V inside a band already; running whole batch elements (sequences) one after
+            // the other, about 48 MiB of K/V at a time, still keeps more of q, k, v and o in L2 and with it
+            // power for the tensor pipe: B=2, Hq=32, Hkv=8, S=8192 1235-1237 against 1223-1225 TFLOP/s; 32 packed
+            // prompts of 1024-8192 tokens 1015-1075 against 989-993 (12 to 20 groups). A packed call gives only
+            // the longest sequence: the others are taken as half as long on average.
+            const long long per_elem = (long long)p.kv_heads * kv_bytes_per_stream / (p.mode == MODE_VARLEN ? 2 : 1);
             const long long elems = std::max<long long>(1, (48LL << 20) / per_elem);
             groups = (int)((p.num_seqs + elems - 1) / elems);
         }
